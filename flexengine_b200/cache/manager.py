@@ -9,8 +9,9 @@ needs share neither a page size nor a lifetime.
 A request's pages are given back when it ends (allocator.py:103-105) or, in a window
 group, once the window has passed them.  ``reserve`` is atomic across groups.
 
-Storage of a paged group: ``[slots, 2, pages, kv_heads, page_size, head_dim]`` (keys at
-index 0, values at 1), so one (page, head) tile is contiguous.
+Storage of a paged group: ``[slots, planes, pages, kv_heads, page_size, head_dim]`` (keys at
+index 0, values at 1; a group of one plane keeps a single vector per token that serves as both), so one
+(page, head) tile is contiguous.
 """
 from __future__ import annotations
 
@@ -40,7 +41,8 @@ class PagedGroup:
         self.spec = spec
         self.page_size = int(page_size)
         self.pool = PagePool(num_pages)
-        self.storage = torch.zeros((spec.slots, 2, num_pages, spec.kv_heads, self.page_size, spec.head_dim),
+        self.planes = int(getattr(spec, "planes", 2))
+        self.storage = torch.zeros((spec.slots, self.planes, num_pages, spec.kv_heads, self.page_size, spec.head_dim),
                                    dtype=dtype, device=device)
         # the block tables once more, as one matrix with a row per seat (a request's state slot): what a step's
         # metadata is gathered from with a few array operations instead of a loop over requests and pages
@@ -59,10 +61,10 @@ class PagedGroup:
         self.table_rows[seat, first:] = RELEASED
 
     def kv_slot(self, slot: int):
-        return self.storage[slot, 0], self.storage[slot, 1]
+        return self.storage[slot, 0], self.storage[slot, self.planes - 1]
 
     def bytes_per_token(self) -> int:
-        return 2 * self.spec.slots * self.spec.kv_heads * self.spec.head_dim * self.storage.element_size()
+        return self.planes * self.spec.slots * self.spec.kv_heads * self.spec.head_dim * self.storage.element_size()
 
 
 class StateGroup:

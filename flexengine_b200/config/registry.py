@@ -18,15 +18,18 @@ class Architecture:
     name: str
     config_class: type
     build_plan: Callable
+    refine: Callable | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, config_class: type, build_plan: Callable) -> None:
+def register_architecture(name: str, config_class: type, build_plan: Callable, refine: Callable | None = None) -> None:
     """Make an architecture known.  ``config_class.from_dict(dict)`` must build the typed
-    config; ``build_plan(config)`` must return a ModelPlan."""
-    _ARCHITECTURES[name] = Architecture(name, config_class, build_plan)
+    config; ``build_plan(config)`` must return a ModelPlan.  ``refine(config, shapes)``, where an
+    architecture has sizes that only a checkpoint's tensor shapes give, returns the plan for a checkpoint
+    with tensors ``shapes`` {name: shape}; the loader calls it once it has read the checkpoint's index."""
+    _ARCHITECTURES[name] = Architecture(name, config_class, build_plan, refine)
 
 
 def known_architectures() -> list[str]:
@@ -42,6 +45,8 @@ def _load_builtin() -> None:
 def architecture_of(config: Mapping) -> Architecture:
     _load_builtin()
     archs = config.get("architectures")
+    if not archs and isinstance(config.get("architecture"), str):
+        archs = [config["architecture"]]            # some designs name themselves with one string
     if not archs or not isinstance(archs, (list, tuple)):
         raise ConfigError("config.json: key 'architectures' is missing or empty; known architectures: "
                           + ", ".join(sorted(_ARCHITECTURES)))
@@ -51,11 +56,12 @@ def architecture_of(config: Mapping) -> Architecture:
     return _ARCHITECTURES[name]
 
 
-def resolve(config: Mapping):
-    """config.json contents -> (typed config, ModelPlan)."""
+def resolve(config: Mapping, shapes: Mapping | None = None):
+    """config.json contents -> (typed config, ModelPlan); with ``shapes`` {tensor name: shape} of a checkpoint, an
+    architecture that reads sizes from there does."""
     arch = architecture_of(config)
     typed = arch.config_class.from_dict(config)
-    plan = arch.build_plan(typed)
+    plan = arch.refine(typed, shapes) if (shapes is not None and arch.refine is not None) else arch.build_plan(typed)
     plan.validate()
     return typed, plan
 

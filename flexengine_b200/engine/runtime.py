@@ -543,7 +543,7 @@ def pages_that_fit(plan, config: EngineConfig, dtype) -> int:
         raise ValueError("kv_num_blocks=0 (size the pool from free memory) needs a CUDA device")
     free, _total = torch.cuda.mem_get_info(torch.device(config.device))
     width = torch.empty((), dtype=dtype).element_size()
-    page_bytes = sum(2 * g.slots * g.kv_heads * g.head_dim * (g.page_size or config.kv_block_size) * width
+    page_bytes = sum(getattr(g, "planes", 2) * g.slots * g.kv_heads * g.head_dim * (g.page_size or config.kv_block_size) * width
                      for g in plan.cache_groups if g.kind != "state")
     pages = int(free * config.kv_memory_fraction) // max(page_bytes, 1)
     smallest = min((g.page_size or config.kv_block_size for g in plan.cache_groups if g.kind != "state"),

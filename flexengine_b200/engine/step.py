@@ -41,7 +41,8 @@ class GroupView:
         self.max_pages = 0
 
     def kv_slot(self, slot: int):
-        return self.storage[slot, 0], self.storage[slot, 1]
+        """(keys, values) of one cache slot; a group of one plane hands out that plane twice."""
+        return self.storage[slot, 0], self.storage[slot, self.storage.shape[1] - 1]
 
     def state(self, slot: int):
         """[max_requests, *state_shape] storage of one state slot layer; index with ctx.state_slots."""

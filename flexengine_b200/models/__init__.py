@@ -1,1 +1,1 @@
-from . import qwen2  # noqa: F401  (registers Qwen2ForCausalLM)
+from . import fuvozen, qwen2  # noqa: F401  (register Fuvozen and Qwen2ForCausalLM)

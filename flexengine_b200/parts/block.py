@@ -121,4 +121,53 @@ def _norm(norm, ctx, residual, delta, upcoming):
     return norm.forward(ctx, residual, delta)
 
 
+class DepthWeights:
+    """The learned weights with which a layer blends all streams so far; a part, so that it is bound by name."""
+
+    def __init__(self, count: int):
+        self.count = int(count)
+        self.weight = None
+
+    def parameter_shapes(self) -> dict:
+        return {"weight": ((self.count,), "vector")}
+
+    def bind(self, tensors: dict) -> None:
+        from .base import Part
+        Part.bind(self, tensors)
+
+    def reads_first(self):
+        return None
+
+
+class ParallelDepthAverageBlock:
+    """One norm whose output feeds mixer and feed-forward side by side, then a learned average over depth:
+        h = norm(x);  X_{i+1} = x + (mixer(h) + feed_forward(h));  x <- sum_{j=0..i+1} a_j X_j,
+    with X_0 the embedding's output and i = ``depth`` the layer's place in the stack (``block_params``).  The X_j of a
+    step are kept in one float32 tensor [layers + 1, T, width] that the first layer makes; sum and average are
+    float32 and one kernel.  A layer may have no feed-forward."""
+    part_names = ("norm", "mixer", "feed_forward", "depth_average")
+
+    def __init__(self, layer_spec):
+        params = dict(layer_spec.block_params)
+        self.depth, self.total = int(params["depth"]), int(params["total"])
+        self.norm = build_part("norm", layer_spec.norm)
+        self.mixer = build_part("mixer", layer_spec.mixer)
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward) if layer_spec.feed_forward is not None else None
+        self.depth_average = DepthWeights(self.depth + 2)
+
+    def parts(self) -> dict:
+        return {name: getattr(self, name) for name in self.part_names if getattr(self, name) is not None}
+
+    def forward(self, ctx, residual, pending, entry):
+        h = self.norm.forward(ctx, residual, pending)
+        mixed = self.mixer.forward(ctx, h, entry)
+        fed = self.feed_forward.forward(ctx, h) if self.feed_forward is not None else None
+        if self.depth == 0 or "stream_history" not in ctx.__dict__:
+            ctx.__dict__["stream_history"] = torch.empty((self.total + 1,) + tuple(residual.shape), dtype=torch.float32,
+                                                         device=residual.device)
+        ctx.ops.depth_average(ctx.__dict__["stream_history"], residual, mixed, fed, self.depth_average.weight, self.depth)
+        return None
+
+
 register_block("prenorm", PreNormBlock)
+register_block("parallel_depth_average", ParallelDepthAverageBlock)

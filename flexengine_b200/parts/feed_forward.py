@@ -33,4 +33,65 @@ class SwiGLU(FeedForward):
         return ctx.ops.linear(act, self.down_weight, follow=follow, upcoming=upcoming)
 
 
+class XieluMlp(FeedForward):
+    """down( act(up(h)) ) with the two-sided activation xIELU of two learned numbers p, q:
+    z > 0: softplus(p) z^2 + z/2;   z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.up_weight = self.down_weight = self.act = None
+
+    def parameter_shapes(self) -> dict:
+        h, i = self.hidden_size, self.intermediate_size
+        return {"up.weight": ((i, h), "matrix"), "down.weight": ((h, i), "matrix"), "act": ((2,), "vector")}
+
+    def reads_first(self):
+        return self.up_weight
+
+    def forward(self, ctx, h):
+        ops = ctx.ops
+        return ops.linear(ops.activation(ops.linear(h, self.up_weight), "xielu", self.act), self.down_weight)
+
+
+class RoutedExperts(FeedForward):
+    """A mixture of small gated feed-forward layers: every token runs its ``top`` best experts of ``experts``.
+
+    Router logits z = W_router h and s = softmax(z) over all experts in float32; the ``top`` largest s are
+    chosen and used as weights, times ``scale``, not renormalised; the output is the weighted sum of the chosen
+    experts' down( silu(gate h) * up h ), plus a shared expert of the same form (size ``shared_size``, 0 for
+    none) that every token runs.  Tokens are sorted by expert on the device and each expert multiplies its own
+    rows (``ops.routed_experts``): no count ever comes back to the host, so the step can be a CUDA graph."""
+
+    def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, scale: float = 1.0, shared_size: int = 0):
+        self.hidden_size, self.experts, self.top = int(hidden_size), int(experts), int(top)
+        self.expert_size, self.scale, self.shared_size = int(expert_size), float(scale), int(shared_size)
+        self.router_weight = self.experts_gate_up_weight = self.experts_down_weight = None
+        self.shared_gate_up_weight = self.shared_down_weight = None
+
+    def parameter_shapes(self) -> dict:
+        h, e, f = self.hidden_size, self.experts, self.expert_size
+        shapes = {"router.weight": ((e, h), "float32"), "experts.gate_up.weight": ((e * 2 * f, h), "matrix"),
+                  "experts.down.weight": ((e * h, f), "matrix")}
+        if self.shared_size:
+            shapes["shared.gate_up.weight"] = ((2 * self.shared_size, h), "matrix")
+            shapes["shared.down.weight"] = ((h, self.shared_size), "matrix")
+        return shapes
+
+    def reads_first(self):
+        return self.router_weight
+
+    def forward(self, ctx, h):
+        ops = ctx.ops
+        e, f, d = self.experts, self.expert_size, self.hidden_size
+        logits = ops.linear(h, self.router_weight, None, out_float32=True)
+        chosen, weights = ops.route_top(logits, self.top, self.scale)
+        shared = None
+        if self.shared_size:
+            shared = ops.linear(ops.linear_swiglu(h, self.shared_gate_up_weight, self.shared_size), self.shared_down_weight)
+        return ops.routed_experts(h, chosen, weights, self.experts_gate_up_weight.view(e, 2 * f, d),
+                                  self.experts_down_weight.view(e, d, f), shared)
+
+
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("xielu_mlp", XieluMlp)
+register_feed_forward("routed_experts", RoutedExperts)

@@ -34,4 +34,22 @@ class RMSNorm(Norm):
         return None
 
 
+class GroupRMSNorm(Norm):
+    """RMSNorm in groups: a row is cut into ``groups`` equal consecutive parts, each divided by its own
+    sqrt(mean(part^2) + eps); the whole is then multiplied by the weight.  One group is the plain norm."""
+
+    def __init__(self, hidden_size: int, eps: float, groups: int = 1):
+        self.hidden_size, self.eps, self.groups = int(hidden_size), float(eps), int(groups)
+        if self.groups < 1 or self.hidden_size % self.groups:
+            raise ValueError("the number of norm groups must divide the width")
+        self.weight = None
+
+    def parameter_shapes(self) -> dict:
+        return {"weight": ((self.hidden_size,), "vector")}
+
+    def forward(self, ctx, residual, delta, rows=None):
+        return ctx.ops.add_group_rmsnorm(residual, delta, self.weight, self.eps, self.groups, ctx.dtype, rows)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("group_rmsnorm", GroupRMSNorm)

@@ -34,6 +34,8 @@ class CacheGroupSpec:
     ``chunk_granularity``: portions of a prompt that do not end it must be multiples of this many
     tokens (a mixer whose state advances in blocks); the scheduler rounds to the least common
     multiple over the groups.
+    ``planes``: how many tensors a paged group keeps per token: 2 (keys and values) or 1 (a mixer whose
+    keys and values are made of one cached vector).
     """
     name: str
     kind: str
@@ -45,8 +47,11 @@ class CacheGroupSpec:
     state_dtype: str = "float32"
     page_size: int = 0
     chunk_granularity: int = 1
+    planes: int = 2
 
     def __post_init__(self):
+        if self.planes not in (1, 2):
+            raise ValueError("a paged group keeps one or two tensors per token")
         if self.page_size < 0 or self.chunk_granularity < 1:
             raise ValueError("page_size must be >= 0 and chunk_granularity >= 1")
         if self.kind not in ("full", "window", "state"):
@@ -57,11 +62,14 @@ class CacheGroupSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: which parts it is made of.  ``block`` names the arrangement."""
+    """One layer: which parts it is made of.  ``block`` names the arrangement, ``block_params`` what the
+    arrangement itself needs to know (its depth in the stack, for instance); ``feed_forward`` may be None for a
+    layer without one, where the arrangement allows it."""
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None
     norm: PartSpec
     block: str = "prenorm"
+    block_params: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -95,7 +103,8 @@ class WeightBinding:
     storage instead (tied embeddings); then ``sources`` is empty, and ``absent`` may name
     checkpoint tensors whose presence contradicts the alias (``why`` says what they contradict).
     ``kind`` is "matrix" (kept in the compute dtype, bfloat16 or as stored when 32-bit),
-    "vector" (norm weights and biases; held in float32, which is lossless) or
+    "vector" (norm weights and biases; held in float32, which is lossless), "float32" (a matrix
+    whose product is taken in 32-bit whatever the compute dtype: a router, a decay's projections) or
     "int" (integer tables, int32).
     """
     target: tuple

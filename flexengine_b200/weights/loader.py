@@ -76,7 +76,7 @@ def _natural(name: str):
 def _held_dtype(kind: str, stored: list, compute: torch.dtype) -> torch.dtype:
     if kind == "int":
         return torch.int32
-    if kind == "vector" or compute == torch.float32:
+    if kind in ("vector", "float32") or compute == torch.float32:
         return torch.float32
     if any(s == "F32" for s in stored):
         return torch.float32          # stored in 32-bit: stays so
@@ -122,8 +122,8 @@ def _bind_all(plan, compute: torch.dtype, device, fetch, stored_dtype) -> Decode
 def load_model(model_dir: str, dtype: str = "bfloat16", device="cuda:0"):
     """Model folder -> (typed config, plan, DecoderModel with weights on ``device``)."""
     compute = COMPUTE_DTYPES[dtype]
-    typed, plan = resolve(read_config_json(model_dir))
     reader = CheckpointReader(model_dir)
+    typed, plan = resolve(read_config_json(model_dir), {name: tuple(e.shape) for name, e in reader.entries.items()})
     check_against_plan(plan, reader.entries)
     try:
         model = _bind_all(plan, compute, device, lambda name, _shape: reader.read(name),

@@ -117,6 +117,179 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
     return out
 
 
+# ---- hashed pair embedding, grouped norm, depth average ----------------------------------------------
+def embedding_hashed_pairs(token_ids, table, pair_table, previous, state_slots, cu_q, q_start, token_request,
+                           buckets, mul_prev, mul_cur):
+    """table[token] + pair_table[(previous token * mul_prev + token * mul_cur) % buckets], row ``buckets`` at
+    position 0; ``previous`` [seats, 1] holds every seat's last token and is brought up to date."""
+    out = table[token_ids.long()].float()
+    cu, starts, seats = cu_q.tolist(), q_start.tolist(), state_slots.tolist()
+    for r in range(len(starts)):
+        a, b = cu[r], cu[r + 1]
+        tokens = token_ids[a:b].long()
+        before = torch.zeros_like(tokens)
+        before[1:] = tokens[:-1]
+        if starts[r] > 0 and seats[r] >= 0:
+            before[0] = previous[seats[r], 0]
+        rows = (before * mul_prev + tokens * mul_cur) % buckets
+        if starts[r] == 0:
+            rows[0] = buckets
+        out[a:b] += pair_table[rows].float()
+        if seats[r] >= 0:
+            previous[seats[r], 0] = tokens[-1].to(previous.dtype)
+    return out
+
+
+def add_group_rmsnorm(residual, delta, weight, eps, groups, out_dtype, rows=None):
+    if rows is None:
+        if delta is not None:
+            residual += delta.float()
+        x = residual
+    else:
+        x = residual[rows.long()]
+        if delta is not None:
+            x = x + delta[rows.long()].float()
+    n, width = x.shape
+    parts = x.view(n, groups, width // groups)
+    parts = parts * torch.rsqrt(parts.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return (parts.reshape(n, width) * weight.float()).to(out_dtype)
+
+
+def depth_average(history, x, mixed, fed, alpha, depth):
+    """history[depth + 1] = x + (mixed + fed); x <- sum_j alpha[j] history[j], j = 0 .. depth + 1 (history[0] = x first
+    when depth is 0).  All float32."""
+    if depth == 0:
+        history[0].copy_(x)
+    delta = mixed.float() if fed is None else mixed.float() + fed.float()
+    history[depth + 1].copy_(x + delta)
+    total = torch.zeros_like(x)
+    for j in range(depth + 2):
+        total += alpha[j] * history[j]
+    x.copy_(total)
+
+
+# ---- linear-recurrent mixer ---------------------------------------------------------------------------
+def token_shift_blend(h, mu, state, offset, state_slots, cu_q, token_request):
+    """Five blends h + (h' - h) * mu_s with h' the row before (the seat's kept row for a portion's first token);
+    returns ([4, T, D] in h's dtype, [T, D] float32) and keeps every seat's last row in state[seat, offset:]."""
+    T, D = h.shape
+    hf = h.float()
+    before = torch.zeros_like(hf)
+    cu, seats = cu_q.tolist(), state_slots.tolist()
+    for r in range(len(seats)):
+        a, b = cu[r], cu[r + 1]
+        before[a + 1:b] = hf[a:b - 1]
+        if seats[r] >= 0:
+            before[a] = state[seats[r], offset:offset + D]
+            state[seats[r], offset:offset + D] = hf[b - 1]
+    mus = mu.float().view(5, D)
+    blends = hf[None] + (before - hf)[None] * mus[:, None, :]
+    return blends[:4].to(h.dtype).contiguous(), blends[4].contiguous()
+
+
+def activation(x, kind, params=None):
+    z = x.float()
+    if kind == "tanh":
+        y = torch.tanh(z)
+    elif kind == "xielu":
+        p, q = params.float()
+        ap, an = torch.log1p(torch.exp(p)), 0.5 + torch.log1p(torch.exp(q))
+        y = torch.where(z > 0, ap * z * z + 0.5 * z, an * (torch.exp(torch.clamp(z, max=0.0)) - 1.0 - z) + 0.5 * z)
+    else:
+        raise ValueError(kind)
+    return y.to(x.dtype)
+
+
+def wkv_recurrence(r, k, v, decay_logits, w0, u, state, state_slots, cu_q, heads, dim):
+    T = r.shape[0]
+    rf, kf, vf = (t.float().view(T, heads, dim) for t in (r, k, v))
+    decay = torch.exp(-torch.exp(decay_logits.float() + w0.float())).view(T, heads, dim)
+    bonus = u.float().view(heads, dim)
+    out = torch.zeros(T, heads, dim, dtype=torch.float32, device=r.device)
+    cu, seats = cu_q.tolist(), state_slots.tolist()
+    n = heads * dim * dim
+    for i in range(len(seats)):
+        S = state[seats[i], :n].view(heads, dim, dim).clone() if seats[i] >= 0 else torch.zeros(heads, dim, dim)
+        for t in range(cu[i], cu[i + 1]):
+            kv = kf[t][:, :, None] * vf[t][:, None, :]
+            out[t] = torch.einsum("hi,hij->hj", rf[t], S + bonus[:, :, None] * kv)
+            S = decay[t][:, :, None] * S + kv
+        if seats[i] >= 0:
+            state[seats[i], :n] = S.reshape(-1)
+    return out.view(T, heads * dim)
+
+
+def head_rmsnorm_gate(out, weight, g, eps, heads, out_dtype):
+    T, inner = out.shape
+    x = out.float().view(T, heads, inner // heads)
+    x = x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps)
+    gf = g.float()
+    return (x.reshape(T, inner) * weight.float() * (gf / (1.0 + torch.exp(-gf)))).to(out_dtype)
+
+
+# ---- attention over a cached latent -------------------------------------------------------------------
+def batched_linear(x, w, token_major=False):
+    """x [B, M, K] (any strides) times w [B, N, K]^T -> [B, M, N], or [M, B N] with ``token_major``."""
+    y = torch.einsum("bmk,bnk->bmn", x.float(), w.float()).to(x.dtype)
+    if token_major:
+        return y.transpose(0, 1).reshape(x.shape[1], -1).contiguous()
+    return y
+
+
+def latent_prepare(q, q_latent, down, norm_weight, eps, positions, inv_freq, rot_dims, slot_mapping, rows,
+                   heads, dim, rot_dim, rank, row, page_size):
+    T = q.shape[0]
+    qf = q.float().view(T, heads, dim + rot_dim)
+    ang = positions.float()[:, None] * inv_freq.float()[None, :]
+    cos, sin = ang.cos(), ang.sin()
+
+    def turn(x):                                   # x [..., rot_dim], pairs (2i, 2i + 1) of the first rot_dims
+        y = x.clone()
+        a, b = x[..., 0:rot_dims:2], x[..., 1:rot_dims:2]
+        c, s = (cos, sin) if x.dim() == 2 else (cos[:, None, :], sin[:, None, :])
+        y[..., 0:rot_dims:2] = a * c - b * s
+        y[..., 1:rot_dims:2] = b * c + a * s
+        return y
+
+    queries = torch.zeros(T, heads, row, dtype=torch.float32, device=q.device)
+    queries[:, :, :rank] = q_latent.float().transpose(0, 1)
+    queries[:, :, rank:rank + rot_dim] = turn(qf[:, :, dim:])
+    latent = down.float()[:, :rank]
+    latent = latent * torch.rsqrt(latent.pow(2).mean(dim=-1, keepdim=True) + eps) * norm_weight.float()
+    cached = torch.zeros(T, row, dtype=torch.float32, device=q.device)
+    cached[:, :rank] = latent
+    cached[:, rank:rank + rot_dim] = turn(down.float()[:, rank:])
+    if slot_mapping is not None:
+        slots = slot_mapping.long()
+        keep = slots >= 0
+        rows[slots[keep] // page_size, 0, slots[keep] % page_size] = cached[keep].to(rows.dtype)
+    return queries.view(T, heads * row).to(q.dtype)
+
+
+# ---- routed feed-forward ------------------------------------------------------------------------------
+def route_top(logits, top, scale):
+    scores = torch.softmax(logits.float(), dim=-1)
+    best = torch.topk(scores, top, dim=-1)
+    return best.indices.to(torch.int32), (best.values * scale).float()
+
+
+def routed_experts(h, chosen, weights, gate_up, down, shared=None):
+    T, D = h.shape
+    f = down.shape[2]
+    total = torch.zeros(T, D, dtype=torch.float32, device=h.device)
+    hf = h.float()
+    for slot in range(chosen.shape[1]):                   # a token's experts are added in the order they were chosen
+        for e in chosen[:, slot].unique().tolist():
+            rows = (chosen[:, slot] == e).nonzero().flatten()
+            gu = hf[rows] @ gate_up[e].float().T
+            g, u = gu[:, :f], gu[:, f:]
+            act = (g / (1.0 + torch.exp(-g)) * u).to(h.dtype).float()
+            total[rows] += weights[rows, slot, None] * (act @ down[e].float().T)
+    if shared is not None:
+        total += shared.float()
+    return total.to(h.dtype)
+
+
 # ---- sampling ----------------------------------------------------------------------------------
 MASK64 = (1 << 64) - 1
 
