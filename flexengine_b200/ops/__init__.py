@@ -621,6 +621,207 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
                              ctx.max_q_len, nq, nkv, d, page_size, scale, window)
 
 
+# ---- the stream: hashed pair embedding, grouped norm, average over depth, activations ---------------------------
+def embedding_hashed_pairs(token_ids, table, pair_table, previous, state_slots, cu_q, q_start, token_request,
+                           buckets, mul_prev, mul_cur):
+    """float32 rows [T, H] = table[token] + pair_table[(previous token * mul_prev + token * mul_cur) mod buckets], the
+    table's last row (``buckets``) at position 0.  ``previous`` (int32 [seats, 1]) holds every seat's last token of the
+    step before and is brought up to date; a seat below 0 keeps nothing."""
+    _need_cuda(token_ids, table, pair_table, previous, state_slots, cu_q, q_start, token_request)
+    T, (V, H) = token_ids.numel(), table.shape
+    if previous.dtype != torch.int32 or not previous.is_contiguous() or pair_table.dtype != table.dtype \
+            or tuple(pair_table.shape) != (buckets + 1, H):
+        raise ValueError("embedding_hashed_pairs: previous is int32 [seats, 1]; the pair table is [buckets + 1, H] in the table's dtype")
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _run(_core(), "fe_embedding_hashed_pairs", _ptr(token_ids), _ptr(table), _ptr(pair_table), _ptr(previous), _ptr(state_slots),
+         _ptr(cu_q), _ptr(q_start), _ptr(token_request), _ptr(out), _c_int(T), _c_int(H), _c_int(V), _c_int(buckets),
+         _c_ll(mul_prev), _c_ll(mul_cur), _c_int(previous.shape[0]), _c_int(_code(table.dtype)),
+         _ptr(status_word(table.device)), _stream())
+    return out
+
+
+def add_group_rmsnorm(residual, delta, weight, eps, groups, out_dtype, rows=None):
+    """Fused residual add + RMSNorm in ``groups`` equal consecutive parts of a row, each with its own root mean square;
+    ``rows`` as in ``add_rmsnorm``."""
+    _need_cuda(residual, delta, weight, rows)
+    T, H = residual.shape
+    if residual.dtype != torch.float32 or weight.dtype != torch.float32 or not residual.is_contiguous():
+        raise TypeError("the residual stream and norm weights are float32")
+    if delta is not None and (delta.dtype != out_dtype or delta.shape != residual.shape or not delta.is_contiguous()):
+        raise ValueError("add_group_rmsnorm: delta must be contiguous, shaped like the residual, in the compute dtype")
+    n_out = T if rows is None else rows.numel()
+    out = torch.empty((n_out, H), dtype=out_dtype, device=residual.device)
+    _run(_core(), "fe_add_group_rmsnorm", _ptr(residual), _ptr(delta), _ptr(weight), _c_float(eps), _ptr(out), _ptr(rows),
+         _c_int(n_out), _c_int(H), _c_int(groups), _c_int(T), _c_int(_code(out_dtype)), _stream())
+    return out
+
+
+def depth_average(history, x, mixed, fed, alpha, depth):
+    """history[depth + 1] = x + (mixed + fed); x <- sum_j alpha[j] history[j] over j = 0 .. depth + 1, in place, float32.
+    history [layers + 1, T, H] float32 (entry 0 is set to x first when depth is 0); ``fed`` may be None."""
+    _need_cuda(history, x, mixed, fed, alpha)
+    if history.dtype != torch.float32 or x.dtype != torch.float32 or alpha.dtype != torch.float32 or not x.is_contiguous() \
+            or not history.is_contiguous() or tuple(history.shape[1:]) != tuple(x.shape) or history.shape[0] < depth + 2 \
+            or alpha.numel() < depth + 2:
+        raise ValueError("depth_average: float32 stream [T, H], history [>= depth + 2, T, H], at least depth + 2 weights")
+    for branch in (mixed, fed):
+        if branch is not None and (branch.shape != x.shape or not branch.is_contiguous() or branch.dtype != mixed.dtype):
+            raise ValueError("depth_average: the branches are contiguous, shaped like the stream, of one dtype")
+    _run(_core(), "fe_depth_average", _ptr(history), _ptr(x), _ptr(mixed), _ptr(fed), _ptr(alpha), _c_int(depth),
+         _c_ll(x.numel()), _c_int(_code(mixed.dtype)), _stream())
+
+
+ACTIVATIONS = {"tanh": 0, "xielu": 1}
+
+
+def activation(x, kind, params=None):
+    """Elementwise, float arithmetic, the input's dtype out: "tanh", or "xielu" with params = (p, q) on the device:
+    z > 0: softplus(p) z^2 + z/2; z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2."""
+    _need_cuda(x, params)
+    if kind not in ACTIVATIONS:
+        raise ValueError(f"unknown activation {kind!r}; known: {sorted(ACTIVATIONS)}")
+    if not x.is_contiguous() or (params is not None and (params.dtype != torch.float32 or params.numel() < 2)):
+        raise ValueError("activation: a contiguous tensor; parameters are two float32 numbers")
+    out = torch.empty_like(x)
+    _run(_core(), "fe_activation", _ptr(x), _ptr(out), _c_ll(x.numel()), _c_int(ACTIVATIONS[kind]), _ptr(params),
+         _c_int(_code(x.dtype)), _stream())
+    return out
+
+
+# ---- the linear-recurrent mixer ---------------------------------------------------------------------------------
+def token_shift_blend(h, mu, state, offset, state_slots, cu_q, token_request):
+    """The five blends h + (h' - h) * mu_s of every token with the row before it; a portion's first token takes the row
+    its seat kept (``state[seat, offset : offset + H]``, float32), which then becomes this step's last row.  Returns
+    ([4, T, H] in h's dtype, [T, H] float32): the blends of the four projections and of the decay."""
+    _need_cuda(h, mu, state, state_slots, cu_q, token_request)
+    T, H = h.shape
+    if mu.dtype != torch.float32 or mu.numel() != 5 * H or state.dtype != torch.float32 or state.stride(1) != 1 or not h.is_contiguous():
+        raise ValueError("token_shift_blend: mu is float32 [5 H]; the state rows are float32 with unit stride")
+    blends = torch.empty((4, T, H), dtype=h.dtype, device=h.device)
+    blend_w = torch.empty((T, H), dtype=torch.float32, device=h.device)
+    _run(_core(), "fe_token_shift_blend", _ptr(h), _ptr(mu), _ptr(state), _c_ll(state.stride(0)), _c_ll(offset), _ptr(state_slots),
+         _ptr(cu_q), _ptr(token_request), _ptr(blends), _ptr(blend_w), _c_int(T), _c_int(H), _c_int(state.shape[0]),
+         _c_int(_code(h.dtype)), _stream())
+    return blends, blend_w
+
+
+def wkv_recurrence(r, k, v, decay_logits, w0, u, state, state_slots, cu_q, heads, dim):
+    """out_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T with w_t = exp(-exp(decay_logits_t + w0)),
+    per request and head; S [dim, dim] float32 lives in ``state[seat, : heads dim dim]`` from step to step.  r, k, v
+    [T, heads dim] in the compute dtype; returns float32 [T, heads dim]."""
+    _need_cuda(r, k, v, decay_logits, w0, u, state, state_slots, cu_q)
+    T, inner = r.shape
+    if inner != heads * dim or decay_logits.dtype != torch.float32 or w0.dtype != torch.float32 or u.dtype != torch.float32 \
+            or state.dtype != torch.float32 or state.stride(1) != 1 or k.dtype != r.dtype or v.dtype != r.dtype \
+            or not (r.is_contiguous() and k.is_contiguous() and v.is_contiguous() and decay_logits.is_contiguous()):
+        raise ValueError("wkv_recurrence: r, k, v contiguous [T, heads dim] of one dtype; decay, w0, u and the state float32")
+    out = torch.empty((T, inner), dtype=torch.float32, device=r.device)
+    _run(_core(), "fe_wkv_recurrence", _ptr(r), _ptr(k), _ptr(v), _ptr(decay_logits), _ptr(w0), _ptr(u), _ptr(state),
+         _c_ll(state.stride(0)), _ptr(state_slots), _ptr(cu_q), _ptr(out), _c_int(cu_q.numel() - 1), _c_int(heads), _c_int(dim),
+         _c_int(state.shape[0]), _c_int(_code(r.dtype)), _stream())
+    return out
+
+
+def head_rmsnorm_gate(out, weight, g, eps, heads, out_dtype):
+    """Every head of ``out`` (float32 [T, heads dim]) divided by its root mean square, times ``weight``, times silu(g)."""
+    _need_cuda(out, weight, g)
+    T, inner = out.shape
+    if out.dtype != torch.float32 or weight.dtype != torch.float32 or g.dtype != out_dtype or g.shape != out.shape \
+            or not (out.is_contiguous() and g.is_contiguous()) or inner % heads:
+        raise ValueError("head_rmsnorm_gate: float32 rows and weight, a gate of the same shape in the compute dtype")
+    y = torch.empty((T, inner), dtype=out_dtype, device=out.device)
+    _run(_core(), "fe_head_rmsnorm_gate", _ptr(out), _ptr(weight), _ptr(g), _ptr(y), _c_float(eps), _c_int(T), _c_int(heads),
+         _c_int(inner // heads), _c_int(_code(out_dtype)), _stream())
+    return y
+
+
+# ---- attention over a cached latent ------------------------------------------------------------------------------
+def batched_linear(x, w, token_major=False):
+    """x [B, M, K] (a view with any row and batch strides, unit stride along K) times w [B, N, K]^T, one small matrix a
+    batch entry (a head).  Returns [B, M, N], or [M, B N] with ``token_major``.  float32 runs the true 32-bit product
+    on CUDA cores; bfloat16 the library's batched product with float accumulation."""
+    _need_cuda(x, w)
+    B, M, K = x.shape
+    N = w.shape[1]
+    if w.shape[0] != B or w.shape[2] != K or x.stride(2) != 1 or w.stride(2) != 1 or x.dtype != w.dtype:
+        raise ValueError(f"batched_linear: shapes {tuple(x.shape)} x {tuple(w.shape)}")
+    if x.dtype == torch.float32:
+        if token_major:
+            out = torch.empty((M, B * N), dtype=torch.float32, device=x.device)
+            ldc, sc = B * N, N
+        else:
+            out = torch.empty((B, M, N), dtype=torch.float32, device=x.device)
+            ldc, sc = N, M * N
+        _run(_core(), "fe_gemm_fp32_batched", _ptr(x), _c_ll(x.stride(1)), _c_ll(x.stride(0)), _ptr(w), _c_ll(w.stride(1)),
+             _c_ll(w.stride(0)), _ptr(out), _c_ll(ldc), _c_ll(sc), _c_int(M), _c_int(N), _c_int(K), _c_int(B), _stream())
+        return out
+    y = torch.bmm(x, w.transpose(1, 2))
+    return y.transpose(0, 1).reshape(M, B * N) if token_major else y
+
+
+def latent_prepare(q, q_latent, down, norm_weight, eps, positions, inv_freq, rot_dims, slot_mapping, rows,
+                   heads, dim, rot_dim, rank, row, page_size):
+    """What a step of attention over a cached latent does around the attention kernel (csrc/latent.cu): the latent
+    through its RMS norm, the shared key part and the heads' query parts rotated (interleaved pairs of the first
+    ``rot_dims`` entries, float32 angles), this step's rows [latent | key part | 0] into their cache slots
+    (``rows`` [pages, 1, page_size, row]; slot_mapping None: no write), and the queries [T, heads row] =
+    [q_latent | rotated query part | 0] per head.  q [T, heads (dim + rot_dim)], q_latent [heads, T, rank] in the
+    compute dtype; down [T, rank + rot_dim] float32."""
+    _need_cuda(q, q_latent, down, norm_weight, positions, inv_freq, slot_mapping, rows)
+    T = q.shape[0]
+    if down.dtype != torch.float32 or norm_weight.dtype != torch.float32 or inv_freq.dtype != torch.float32 \
+            or tuple(q.shape) != (T, heads * (dim + rot_dim)) or tuple(q_latent.shape) != (heads, T, rank) \
+            or tuple(down.shape) != (T, rank + rot_dim) or inv_freq.numel() != rot_dims // 2 \
+            or not (q.is_contiguous() and q_latent.is_contiguous() and down.is_contiguous()):
+        raise ValueError("latent_prepare: shapes or dtypes do not fit")
+    if rows.dtype != q.dtype or tuple(rows.shape[1:]) != (1, page_size, row) or not rows.is_contiguous():
+        raise ValueError("latent_prepare: the cache is contiguous [pages, 1, page_size, row] in the compute dtype")
+    queries = torch.empty((T, heads * row), dtype=q.dtype, device=q.device)
+    _run(_core(), "fe_latent_prepare", _ptr(q), _ptr(q_latent), _ptr(down), _ptr(norm_weight), _c_float(eps), _ptr(positions),
+         _ptr(inv_freq), _c_int(rot_dims), _ptr(slot_mapping), _ptr(rows), _c_ll(rows.shape[0] * page_size), _ptr(queries),
+         _c_int(T), _c_int(heads), _c_int(dim), _c_int(rot_dim), _c_int(rank), _c_int(row), _c_int(_code(q.dtype)),
+         _ptr(status_word(q.device)), _stream())
+    return queries
+
+
+# ---- a routed feed-forward ---------------------------------------------------------------------------------------
+def route_top(logits, top, scale):
+    """(int32 [T, top], float32 [T, top]): per token the ``top`` largest softmax scores over all experts (float32, ties
+    to the lower index) times ``scale``, and their experts."""
+    _need_cuda(logits)
+    T, experts = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise TypeError("route_top: router logits are contiguous float32")
+    chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    _run(_core(), "fe_route_top", _ptr(logits), _ptr(chosen), _ptr(weights), _c_int(T), _c_int(experts), _c_int(top),
+         _c_float(scale), _stream())
+    return chosen, weights
+
+
+def routed_experts(h, chosen, weights, gate_up, down, shared=None):
+    """out[t] = sum_c weights[t, c] * down_e( silu(gate_e h_t) * up_e h_t ) with e = chosen[t, c], plus ``shared`` [T, H] if
+    given; gate_up [experts, 2F, H] ([gate; up] per expert), down [experts, H, F].  The (token, choice) pairs are sorted
+    by expert on the device and every expert multiplies its own rows (csrc/routed.cu): nothing comes back to the host."""
+    _need_cuda(h, chosen, weights, gate_up, down, shared)
+    T, H = h.shape
+    experts, F2, _ = gate_up.shape
+    F, top = F2 // 2, chosen.shape[1]
+    if tuple(gate_up.shape) != (experts, 2 * F, H) or tuple(down.shape) != (experts, H, F) or gate_up.dtype != h.dtype \
+            or down.dtype != h.dtype or not (gate_up.is_contiguous() and down.is_contiguous() and h.is_contiguous()) \
+            or chosen.dtype != torch.int32 or weights.dtype != torch.float32 \
+            or (shared is not None and (shared.dtype != h.dtype or shared.shape != h.shape or not shared.is_contiguous())):
+        raise ValueError("routed_experts: shapes or dtypes do not fit")
+    lib = _core()
+    need = lib.fe_routed_experts_workspace(_c_int(T), _c_int(top), _c_int(experts), _c_int(H), _c_int(F), _c_int(_code(h.dtype)))
+    work = torch.empty(need, dtype=torch.uint8, device=h.device)
+    out = torch.empty((T, H), dtype=h.dtype, device=h.device)
+    _run(lib, "fe_routed_experts", _ptr(h), _ptr(chosen), _ptr(weights), _ptr(gate_up), _ptr(down), _ptr(shared), _ptr(out),
+         _ptr(work), _c_ll(need), _c_int(T), _c_int(top), _c_int(experts), _c_int(H), _c_int(F), _c_int(_code(h.dtype)),
+         _ptr(status_word(h.device)), _stream())
+    return out
+
+
 def sample(logits, temperature, top_k, seed, draw, blocks: int = 0):
     """int32 [R]: one token per row of float32 logits [R, V]; see csrc/sampling.cu.  ``blocks``: how many thread
     blocks (a cluster of 1, 2, 4 or 8) share a row; 0 lets the kernel library choose by the number of rows.  The
