@@ -83,7 +83,9 @@ def latent_attention(h, weights, prefix: str, m, eps: float):
     value = (latent @ weights[prefix + "uv"].T).view(T, H, dv)
     scores = (torch.einsum("qhd,khd->hqk", q_plain, k_plain) + torch.einsum("qhd,kd->hqk", q_rot, k_rot)) * m["scale"]
     distance = positions[:, None] - positions[None, :]
-    visible = (distance >= 0) & (distance < m["mask"]["size"])
+    visible = distance >= 0
+    if m.get("mask"):                            # a sliding window: the token itself and the size - 1 before it
+        visible &= distance < m["mask"]["size"]
     scores = scores.masked_fill(~visible[None], float("-inf"))
     out = torch.einsum("hqk,khd->qhd", torch.softmax(scores, dim=-1), value).reshape(T, H * dv)
     return out @ weights[prefix + "o"].T
