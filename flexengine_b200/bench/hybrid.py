@@ -1,0 +1,203 @@
+"""``--workload fuvozen``: prefill and decode throughput of the Fuvozen design at a few sizes that resemble a real
+model's layers (random weights), beside a Qwen2 decoder of equal width, depth and vocabulary, and, at one size, an
+operation-by-operation table of both: time, the bytes and flops of the work, and how far each operation is from the
+roofline of the measured peaks (time / max(bytes / copy rate, flops / bf16 rate)).
+
+Prefill is one 2,048-token prompt in one step; decode is batch 8 at 2,048 cached tokens, replayed from a CUDA graph.
+The table times every call of the kernel provider with CUDA events around it (a synchronize on both sides), in a
+prefill step and in a decode step run kernel by kernel.
+"""
+from __future__ import annotations
+
+import json
+import types
+
+from .clocks import ClockSampler, load_peaks
+from .timing import Timer
+
+PROMPT, CONTEXT, PAGE, BATCH = 2048, 4096, 16, 8
+
+
+def fuvozen_config(width, layers, vocab, heads, experts=8, top=2):
+    """Alternating layers: the recurrence beside a dense feed-forward, then latent attention beside routed experts.
+    Recurrent heads of 64; attention heads of 64 + 64 rotated over a latent of 64 (a cached row of 128)."""
+    stack = []
+    for i in range(layers):
+        if i % 2 == 0:
+            stack.append({"type": "wkv", "mixer": {"heads": width // 64, "dim": 64}, "mlp": {"kind": "dense", "ff": 4 * width}})
+        else:
+            stack.append({"type": "latent_attention",
+                          "mixer": {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 64, "mask": {"size": 1024},
+                                    "rot": {"base": 10000.0, "dims": 64}, "scale": 128 ** -0.5},
+                          "mlp": {"kind": "moe", "expert": {"ff": width}, "router": {"experts": experts, "top": top, "scale": 1.0},
+                                  "shared": {"ff": width}}})
+    return {"architecture": "Fuvozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 2},
+            "embedding": {"bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 7}}, "layers": stack}
+
+
+def qwen2_config(width, layers, vocab, heads):
+    """The closest existing model at equal size: grouped-query attention with heads of 128 and a SwiGLU feed-forward
+    whose three matrices hold what a Fuvozen layer's feed-forward uses per token on average (about 8 width^2)."""
+    return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=layers, hidden_size=width,
+                num_attention_heads=heads, num_key_value_heads=max(1, heads // 4), head_dim=128,
+                intermediate_size=width * 8 // 3 // 256 * 256, vocab_size=vocab, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                max_position_embeddings=32768, tie_word_embeddings=True, use_sliding_window=False, hidden_act="silu", eos_token_id=None)
+
+
+SIZES = {"1k": (1024, 8, 32000, 8), "2k": (2048, 8, 32000, 16), "4k": (4096, 4, 32000, 32)}
+
+
+class TimedOps:
+    """A kernel provider that forwards to ``ops`` and keeps, per operation, the device time of its calls (CUDA events,
+    a synchronize on both sides) and the bytes of the tensors that go in and come out."""
+
+    def __init__(self, ops, torch):
+        self._ops, self._torch = ops, torch
+        self.rows = {}
+
+    def __getattr__(self, name):
+        if name == "native_layers_usable":             # every operation on its own: no layer as one call
+            raise AttributeError(name)
+        target = getattr(self._ops, name)
+        if not callable(target) or isinstance(target, type) or name in ("check_status", "status_word", "sm_count", "scratch"):
+            return target
+        torch = self._torch
+
+        def timed(*args, **kwargs):
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            out = target(*args, **kwargs)
+            end.record()
+            torch.cuda.synchronize()
+            tensors = [a for a in list(args) + list(kwargs.values()) if torch.is_tensor(a)]
+            tensors += [o for o in (out if isinstance(out, (tuple, list)) else [out]) if torch.is_tensor(o)]
+            seen, nbytes = set(), 0
+            for t in tensors:
+                if t.data_ptr() not in seen:
+                    seen.add(t.data_ptr())
+                    nbytes += t.numel() * t.element_size()
+            flops = 0.0
+            if name in ("linear", "linear_swiglu") and len(args) >= 2:
+                flops = 2.0 * args[0].shape[0] * args[1].shape[0] * args[1].shape[1]
+            elif name == "batched_linear":
+                flops = 2.0 * args[0].shape[0] * args[0].shape[1] * args[0].shape[2] * args[1].shape[1]
+            elif name == "routed_experts":
+                pairs = args[1].numel()
+                flops = 2.0 * pairs * 3 * (args[3].shape[1] // 2) * args[3].shape[2]
+                used = min(args[3].shape[0], pairs)
+                nbytes = nbytes - (args[3].numel() + args[4].numel()) * 2 * (1 - used / args[3].shape[0])
+            elif name in ("paged_attention",):
+                ctx, nq, d = args[4], args[5], args[7]
+                window = args[10]
+                pairs = 0
+                for s, n in zip(ctx.host_starts, ctx.host_lengths):
+                    for p in (s, s + n - 1):
+                        pairs += (min(p + 1, window) if window else p + 1) * n / 2.0
+                flops = 4.0 * nq * d * pairs
+                page, kv = args[8], args[6]
+                keys = sum(min(s + n, (window + n) if window else s + n) for s, n in zip(ctx.host_starts, ctx.host_lengths))
+                nbytes = args[0].numel() * 2 + 2 * args[0].shape[0] * nq * d + keys * kv * d * 2 * (1 if args[1].data_ptr() == args[2].data_ptr() else 2)
+            elif name == "wkv_recurrence":
+                flops = 6.0 * args[0].shape[0] * args[9] * args[10] * args[10]
+                nbytes = args[0].numel() * (3 * args[0].element_size() + 8) + 2 * 4 * (args[8].numel() - 1) * args[9] * args[10] * args[10]
+            row = self.rows.setdefault(name, [0, 0.0, 0.0, 0.0])
+            row[0] += 1
+            row[1] += start.elapsed_time(end) * 1e3
+            row[2] += nbytes
+            row[3] += flops
+            return out
+        return timed
+
+    def table(self, peaks):
+        hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+        out = []
+        for name, (calls, us, nbytes, flops) in sorted(self.rows.items(), key=lambda kv: -kv[1][1]):
+            floor = max(nbytes / hbm, flops / tensor) * 1e6
+            out.append({"op": name, "calls": calls, "us": round(us, 1), "mbytes": round(nbytes / 1e6, 1), "gflop": round(flops / 1e9, 1),
+                        "roofline_us": round(floor, 1), "times_roofline": round(us / floor, 1) if floor > 0 else None})
+        return out
+
+
+def run(args) -> int:
+    import torch
+    from .. import ops
+    from ..cache import CacheManager
+    from ..engine import ModelRunner, StepEntry
+    from ..weights import random_model
+
+    dev = "cuda:0"
+    peaks, peak_source = load_peaks(args.peaks)
+    sampler = ClockSampler().start()
+    timer = Timer(ops)
+    gen = torch.Generator().manual_seed(1)
+    results, tables = {}, {}
+    sizes = [args.size] if getattr(args, "size", None) else list(SIZES)
+
+    def measure(cfg, vocab, provider=None, steps=args.steps, warmup=max(args.warmup, 3)):
+        _typed, plan, model = random_model(cfg, seed=0, dtype="bfloat16", device=dev)
+        cache = CacheManager(plan.cache_groups, (BATCH + 1) * CONTEXT // PAGE, PAGE, BATCH + 1, torch.bfloat16, dev)
+        runner = ModelRunner(model, cache, ops=provider)
+        prompt = torch.randint(0, vocab, (PROMPT,), generator=gen).tolist()
+
+        def prefill_once(i):
+            runner.step([StepEntry(f"p{i}", prompt, [PROMPT - 1])])
+            runner.finish(f"p{i}")
+        if provider is not None:                        # the table: one prefill step and one decode step, kernel by kernel
+            prefill_once(-1)
+            provider.rows.clear()
+            prefill_once(0)
+            prefill_table = provider.table(peaks)
+            rids = [f"d{i}" for i in range(BATCH)]
+            for rid in rids:
+                runner.step([StepEntry(rid, prompt, [])])
+            runner.step([StepEntry(rid, [1], [0]) for rid in rids])
+            provider.rows.clear()
+            runner.step([StepEntry(rid, [2], [0]) for rid in rids])
+            return {"prefill": prefill_table, "decode": provider.table(peaks)}
+        for w in range(3):
+            prefill_once(-1 - w)
+        prefill_ms, _ = timer.timed(prefill_once, 5)
+        runner.enable_decode_graphs(BATCH, CONTEXT)
+        rids = [f"d{i}" for i in range(BATCH)]
+        for rid in rids:
+            runner.step([StepEntry(rid, prompt, [])])
+        feed = torch.randint(0, vocab, (warmup + steps, BATCH), generator=gen).tolist()
+
+        def one(i, base=0):
+            runner.step([StepEntry(rid, [feed[base + i][j]], [0]) for j, rid in enumerate(rids)])
+        for w in range(warmup):
+            one(w)
+        ms, launches = timer.timed(lambda i: one(i, warmup), steps)
+        ops.check_status(dev)
+        weights = model.weight_bytes()
+        del runner, cache, model
+        torch.cuda.empty_cache()
+        return {"prefill_tokens_per_s": round(PROMPT / (prefill_ms / 1e3)), "prefill_ms": round(prefill_ms, 2),
+                "decode_tokens_per_s": round(BATCH / (ms / 1e3)), "decode_ms_per_step": round(ms, 3), "weight_gbytes": round(weights / 1e9, 2),
+                "launches": launches}
+
+    launches = 0
+    for name in sizes:
+        width, layers, vocab, heads = SIZES[name]
+        results[name] = {"fuvozen": measure(fuvozen_config(width, layers, vocab, heads), vocab),
+                         "qwen2": measure(qwen2_config(width, layers, vocab, heads), vocab)}
+        launches += results[name]["fuvozen"].pop("launches") + results[name]["qwen2"].pop("launches")
+    if args.kernels:
+        width, layers, vocab, heads = SIZES[sizes[-1] if getattr(args, "size", None) else "2k"]
+        tables["fuvozen"] = measure(fuvozen_config(width, 2, vocab, heads), vocab, TimedOps(ops, torch))
+        tables["qwen2"] = measure(qwen2_config(width, 2, vocab, heads), vocab, TimedOps(ops, torch))
+    sampler.stop()
+    first = results[sizes[0]]["fuvozen"]
+    line = {"metric": f"decode tokens/s (Fuvozen design, size {sizes[0]}, batch {BATCH}, {PROMPT}-token prompts)",
+            "value": first["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic: random token ids, random weights", "impl": "ours",
+            "config": {"model": "Fuvozen beside Qwen2 at equal width, depth and vocabulary", "sizes": {k: list(v) for k, v in SIZES.items() if k in sizes},
+                       "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT, "kv_page": PAGE, "parallelism": "single GPU",
+                       "peaks": peak_source},
+            "sizes": results, "gpu_launches": launches, "clocks": sampler.summary(timer.windows)}
+    if tables:
+        line["operations"] = tables
+    print(json.dumps(line))
+    return 0

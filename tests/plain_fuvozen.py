@@ -133,10 +133,15 @@ def gated_expert(h, weights, prefix: str):
     return (g * torch.sigmoid(g) * (h @ weights[prefix + "up"].T)) @ weights[prefix + "down"].T
 
 
-def moe_ffn(h, weights, prefix: str, spec):
+def moe_ffn(h, weights, prefix: str, spec, gaps=None):
+    """``gaps`` (a list) receives, per token, how far the last chosen score lies above the best one left out,
+    relative to it: a small gap is a close call that a rounding of h can turn."""
     router = spec["router"]
     scores = torch.softmax(h @ weights[prefix + "router"].T, dim=-1)
     top = torch.topk(scores, router["top"], dim=-1)
+    if gaps is not None and router["top"] < scores.shape[-1]:
+        ranked = torch.sort(scores, dim=-1, descending=True).values
+        gaps.append((ranked[:, router["top"] - 1] - ranked[:, router["top"]]) / ranked[:, router["top"] - 1])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for s, e in zip(top.values[t].tolist(), top.indices[t].tolist()):
@@ -146,8 +151,9 @@ def moe_ffn(h, weights, prefix: str, spec):
     return out
 
 
-def forward_logits(config, weights, ids, layers_out=None):
-    """Logits [T, vocab] of one whole sequence; ``layers_out`` (a list) receives the stream after every layer."""
+def forward_logits(config, weights, ids, layers_out=None, gaps=None):
+    """Logits [T, vocab] of one whole sequence; ``layers_out`` (a list) receives the stream after every layer,
+    ``gaps`` (a list) the routers' gaps per token (see ``moe_ffn``)."""
     ids = torch.as_tensor(ids, dtype=torch.long)
     eps, groups = config["norm"]["eps"], config["norm"]["groups"]
     x = bigram_embedding(config, weights, ids)
@@ -167,7 +173,7 @@ def forward_logits(config, weights, ids, layers_out=None):
         elif mlp["kind"] == "dense":
             fed = dense_ffn(h, weights, p + "mlp.")
         else:
-            fed = moe_ffn(h, weights, p + "mlp.", mlp)
+            fed = moe_ffn(h, weights, p + "mlp.", mlp, gaps)
         history.append(x + (mixed + fed))
         alpha = weights[p + "dwa"]
         x = sum(alpha[j] * history[j] for j in range(i + 2))

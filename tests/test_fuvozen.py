@@ -103,27 +103,43 @@ def make_runner(model_dir, dtype, device, pages, page, seats=4):
     return ModelRunner(model, cache, ops=ops_for(device))
 
 
-def plain_logits(model_dir, ids):
+def plain_logits(model_dir, ids, decided=None):
+    """``decided`` (a list) receives a mask of the rows at which no router made a close call (the last chosen score
+    at least 5 % above the best one left out): bfloat16 may turn a close call, and nothing is asserted there."""
     cfg, weights = plain.read_model_folder(model_dir)
-    return plain.forward_logits(cfg, weights, ids)
+    gaps = []
+    logits = plain.forward_logits(cfg, weights, ids, gaps=gaps)
+    if decided is not None:
+        decided.append(torch.stack(gaps).min(dim=0).values > 0.05 if gaps else torch.ones(len(ids), dtype=torch.bool))
+    return logits
 
 
-def close(got, want, dtype, what):
+def close(got, want, dtype, what, bars=(3e-5, 6e-2), rows=None):
+    """Every row within 3e-5 (float32) or 6e-2 (bfloat16) of its own spread (rows differ in size by orders of
+    magnitude where one token is made to stand out), with a tenth of the overall spread as the floor.  ``rows``: a
+    mask of the rows that are compared in bfloat16 (float32 compares all)."""
     got, want = got.float().cpu(), want.float().cpu()
     assert got.shape == want.shape, what
     assert torch.isfinite(got).all(), what
-    spread = float(want.std())
-    err = float((got - want).abs().max())
-    bar = (3e-5 if dtype == "float32" else 6e-2) * max(spread, 1e-3)
-    assert err <= bar, f"{what}: max |diff| {err:.3e} > {bar:.3e} (spread {spread:.3e})"
+    want2, got2 = want.reshape(-1, want.shape[-1]), got.reshape(-1, want.shape[-1])
+    floor = max(0.1 * float(want2.std()), 1e-3)
+    scale = torch.clamp(want2.std(dim=-1), min=floor)
+    err = (got2 - want2).abs().max(dim=-1).values / scale
+    if rows is not None and dtype != "float32":
+        assert int(rows.sum()) >= 0.7 * len(rows), f"{what}: too many close calls for the comparison to mean anything"
+        err = torch.where(rows, err, torch.zeros_like(err))
+    bar = bars[0] if dtype == "float32" else bars[1]
+    worst = int(err.argmax())
+    assert float(err[worst]) <= bar, f"{what}: row {worst} is off by {float(err[worst]):.3e} of its spread (bar {bar:.0e})"
 
 
 def compare(model_dir, results, requests, dtype, what):
     for rid, ids in requests.items():
-        want = plain_logits(model_dir, ids)
+        decided = []
+        want = plain_logits(model_dir, ids, decided)
         rows = sorted(p for (r, p) in results if r == rid)
         assert rows == list(range(len(ids))), f"{what}: request {rid} misses rows"
-        close(torch.stack([results[(rid, p)] for p in rows]), want, dtype, f"{what} request {rid}")
+        close(torch.stack([results[(rid, p)] for p in rows]), want, dtype, f"{what} request {rid}", rows=decided[0])
 
 
 def requests_for(name, seed=3):
@@ -361,7 +377,8 @@ def test_wkv_remembers_over_hundreds_of_tokens(device, dtype):
     silent[3] = h[2]
     assert (plain.wkv_mixer(silent, weights, "", {"heads": heads, "dim": dim}, 1e-5)[-1] - want[-1]).abs().max() > 0.1 * want[-1].abs().max()
     got = drive_mixer(mixer, spec, h, [2, 60, 130, 2, 100] + [1] * 26, device, dt)
-    close(got, want, dtype, "far memory")
+    # hundreds of roundings add up in a state that forgets nothing: wider bars, still far below a lost state's error
+    close(got, want, dtype, "far memory", bars=(2e-4, 0.25))
 
 
 def latent_weights(D, m, seed):
@@ -507,8 +524,9 @@ def test_first_tokens_and_long_decoding(model_dirs, device, dtype):
         if q == len(other) - 1:
             runner.finish("other")
         runner.cache.assert_invariants()
-    close(torch.stack(rows), plain_logits(model_dirs[name], ids), dtype, "long decoding")
-    close(torch.stack(other_rows), plain_logits(model_dirs[name], other), dtype, "the neighbour")
+    decided = []
+    close(torch.stack(rows), plain_logits(model_dirs[name], ids, decided), dtype, "long decoding", rows=decided[0])
+    close(torch.stack(other_rows), plain_logits(model_dirs[name], other, decided), dtype, "the neighbour", rows=decided[1])
     window_group = [g for _, g in runner.cache.paged if g.spec.kind == "window"][0]
     assert window_group.pool.used_pages <= 2                 # 151 tokens under a window of 12 in pages of 16
 
