@@ -101,7 +101,8 @@ class TimedOps:
             elif name == "wkv_recurrence":
                 flops = 6.0 * args[0].shape[0] * args[9] * args[10] * args[10]
                 nbytes = args[0].numel() * (3 * args[0].element_size() + 8) + 2 * 4 * (args[8].numel() - 1) * args[9] * args[10] * args[10]
-            row = self.rows.setdefault(name, [0, 0.0, 0.0, 0.0])
+            shapes = "x".join(str(tuple(a.shape)) for a in args[:2] if torch.is_tensor(a)) if name in ("linear", "linear_swiglu", "batched_linear") else ""
+            row = self.rows.setdefault(f"{name} {shapes}".strip(), [0, 0.0, 0.0, 0.0])
             row[0] += 1
             row[1] += start.elapsed_time(end) * 1e3
             row[2] += nbytes

@@ -61,12 +61,56 @@ gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, const
     }
 }
 
+// The same product for a handful of rows or of columns (decode steps; a router or a low-rank projection): a
+// block of 128 threads owns 8 rows x 16 columns, one output a thread, and walks K in chunks of 64 that it stages in
+// shared memory.  The chain of fused multiply-adds of an output is the one of the kernel above (k ascending from
+// zero, bias added last), so a row's result is the same bit for bit whichever of the two ran.
+constexpr int SR = 8, SC = 16, SK = 64;
+
+__global__ void __launch_bounds__(128)
+gemm_fp32_skinny_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
+                        float* __restrict__ C, int M, int N, int K) {
+    fe::griddep_wait();
+    fe::griddep_launch_dependents();
+    __shared__ float As[SR][SK];
+    __shared__ float Ws[SC][SK + 1];
+    const int tid = threadIdx.x;
+    const int m = tid / SC, n = tid % SC;
+    const int m0 = blockIdx.y * SR, n0 = blockIdx.x * SC;
+    float acc = 0.f;
+    for (int k0 = 0; k0 < K; k0 += SK) {
+#pragma unroll
+        for (int i = 0; i < (SR * SK) / 128; ++i) {
+            const int idx = tid + i * 128;
+            const int r = idx / SK, c = idx % SK;
+            As[r][c] = (m0 + r < M && k0 + c < K) ? A[(size_t)(m0 + r) * K + k0 + c] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < (SC * SK) / 128; ++i) {
+            const int idx = tid + i * 128;
+            const int r = idx / SK, c = idx % SK;
+            Ws[r][c] = (n0 + r < N && k0 + c < K) ? W[(size_t)(n0 + r) * K + k0 + c] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 16
+        for (int k = 0; k < SK; ++k) acc = fmaf(As[m][k], Ws[n][k], acc);
+        __syncthreads();
+    }
+    if (m0 + m < M && n0 + n < N) C[(size_t)(m0 + m) * N + n0 + n] = acc + (bias ? bias[n0 + n] : 0.f);
+}
+
 }  // namespace
 
 extern "C" int fe_gemm_fp32(const float* A, const float* W, const float* bias, float* C, int M, int N, int K,
                             cudaStream_t stream) {
     FE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_fp32: bad sizes M=%d N=%d K=%d", M, N, K);
     if (M == 0) return 0;
+    if (M <= 2 * SR || N <= 128) {                  // few rows, or few columns (the tiles above would be few blocks with long loops)
+        const dim3 few((N + SC - 1) / SC, (M + SR - 1) / SR);
+        FE_REQUIRE(few.y <= 65535, "gemm_fp32: too many rows (%d)", M);
+        fe::launch(gemm_fp32_skinny_kernel, few, 128, 0, stream, A, W, bias, C, M, N, K);
+        return fe_check_launch("gemm_fp32 (few rows)");
+    }
     const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     FE_REQUIRE(grid.y <= 65535, "gemm_fp32: too many rows (%d)", M);
     fe::launch(gemm_fp32_kernel, grid, 256, 0, stream, A, W, bias, C, M, N, K);

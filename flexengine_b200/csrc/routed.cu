@@ -10,6 +10,7 @@
 // its choices.
 #define FE_PDL_CLASS 128
 #include <math_constants.h>
+#include <mma.h>
 
 #include "common.cuh"
 
@@ -199,6 +200,205 @@ routed_product_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_r
     }
 }
 
+// The same products for a handful of rows (a decode step): bound by reading the experts' matrices once.  A tile is up
+// to 8 sorted rows of one expert; a block stages them in shared memory and its 8 warps take 4 output columns each,
+// one after the other: the lanes walk K in 16-byte pieces of the expert's row (and of the paired "up" row when
+// GATED), multiply with all rows, and add up over the warp.
+constexpr int FEW_ROWS = 8, FEW_WARPS = 8, FEW_COLS = 4;
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(FEW_WARPS * 32)
+routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_row, int top, const T* __restrict__ W,
+                          void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
+                          const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K) {
+    griddep_wait();
+    griddep_launch_dependents();
+    if ((int)blockIdx.y >= tiles[0]) return;
+    extern __shared__ __align__(16) unsigned char few_smem[];
+    T* rows_s = reinterpret_cast<T*>(few_smem);                 // [FEW_ROWS][K]
+    const int e = tile_expert[blockIdx.y], row0 = tile_row0[blockIdx.y];
+    const int rows = min(FEW_ROWS, offsets[e + 1] - row0);
+    for (int idx = threadIdx.x; idx < FEW_ROWS * K; idx += blockDim.x) {
+        const int r = idx / K, k = idx % K;
+        T v = from_float<T>(0.f);
+        if (r < rows) {
+            const int src = pair_of_row ? pair_of_row[row0 + r] / top : row0 + r;
+            v = A[(size_t)src * K + k];
+        }
+        rows_s[idx] = v;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const T* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+    constexpr int PIECE = 16 / sizeof(T);                       // elements of a 16-byte piece
+    const bool pieces = K % PIECE == 0;
+    for (int c = 0; c < FEW_COLS; ++c) {
+        const int n = (blockIdx.x * FEW_WARPS + warp) * FEW_COLS + c;
+        if (n >= N) break;
+        const T* wg = We + (size_t)n * K;
+        const T* wu = We + (size_t)(N + n) * K;
+        float acc[FEW_ROWS], acu[GATED ? FEW_ROWS : 1];
+#pragma unroll
+        for (int r = 0; r < FEW_ROWS; ++r) {
+            acc[r] = 0.f;
+            if (GATED) acu[r] = 0.f;
+        }
+        if (pieces) {
+            for (int k = lane * PIECE; k < K; k += 32 * PIECE) {
+                float w[8], u[8], a[8];
+                if (sizeof(T) == 2) {
+                    load8<T>(wg + k, w);
+                    if (GATED) load8<T>(wu + k, u);
+                } else {
+#pragma unroll
+                    for (int x = 0; x < PIECE; ++x) {
+                        w[x] = to_float(wg[k + x]);
+                        if (GATED) u[x] = to_float(wu[k + x]);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < FEW_ROWS; ++r) {
+#pragma unroll
+                    for (int x = 0; x < PIECE; ++x) a[x] = to_float(rows_s[r * K + k + x]);
+#pragma unroll
+                    for (int x = 0; x < PIECE; ++x) {
+                        acc[r] = fmaf(a[x], w[x], acc[r]);
+                        if (GATED) acu[r] = fmaf(a[x], u[x], acu[r]);
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) {
+                const float w = to_float(wg[k]);
+                const float u = GATED ? to_float(wu[k]) : 0.f;
+#pragma unroll
+                for (int r = 0; r < FEW_ROWS; ++r) {
+                    const float a = to_float(rows_s[r * K + k]);
+                    acc[r] = fmaf(a, w, acc[r]);
+                    if (GATED) acu[r] = fmaf(a, u, acu[r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < FEW_ROWS; ++r) {
+            const float g = warp_sum(acc[r]);
+            const float u = GATED ? warp_sum(acu[r]) : 0.f;
+            if (lane == 0 && r < rows) {
+                const size_t at = (size_t)(row0 + r) * N + n;
+                if (GATED) reinterpret_cast<T*>(out)[at] = from_float<T>(g / (1.f + expf(-g)) * u);
+                else reinterpret_cast<float*>(out)[at] = g;
+            }
+        }
+    }
+}
+
+// The two products on tensor cores (bfloat16, float accumulation; mma.sync through the wmma interface).  Tile 64 rows x
+// 64 columns (and the 64 paired "up" columns when GATED), 32 of K a stage, 4 warps with 32 x 32 outputs each.
+constexpr int TBM = 64, TBN = 64, TBK = 32, TLD = TBK + 8;
+
+template <bool GATED>
+__global__ void __launch_bounds__(128)
+routed_product_mma_kernel(const bf16* __restrict__ A, const int* __restrict__ pair_of_row, int top, const bf16* __restrict__ W,
+                          void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
+                          const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K) {
+    using namespace nvcuda;
+    griddep_wait();
+    griddep_launch_dependents();
+    if ((int)blockIdx.y >= tiles[0]) return;
+    __shared__ __align__(32) bf16 As[TBM][TLD];
+    __shared__ __align__(32) bf16 Ws[TBN][TLD];
+    __shared__ __align__(32) bf16 Us[GATED ? TBN : 1][TLD];
+    __shared__ __align__(32) float stage[4][GATED ? 2 : 1][16][20];
+    __shared__ int source[TBM];
+    const int e = tile_expert[blockIdx.y], row0 = tile_row0[blockIdx.y];
+    const int rows = min(TBM, offsets[e + 1] - row0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp >> 1, wn = warp & 1;
+    const int n0 = blockIdx.x * TBN;
+    if (tid < TBM) source[tid] = tid < rows ? (pair_of_row ? pair_of_row[row0 + tid] / top : row0 + tid) : -1;
+    __syncthreads();
+    const bf16* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[2][2], acu[GATED ? 2 : 1][2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            wmma::fill_fragment(acc[i][j], 0.f);
+            if (GATED) wmma::fill_fragment(acu[i][j], 0.f);
+        }
+    const bool pieces = K % 8 == 0;
+    const bf16 zero = __float2bfloat16_rn(0.f);
+    for (int k0 = 0; k0 < K; k0 += TBK) {
+        // 64 rows x 32 columns = 256 pieces of 8 elements per operand, two a thread
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int piece = tid + i * 128;
+            const int r = piece >> 2, c = (piece & 3) * 8;
+            const int src = source[r], gn = n0 + r, gk = k0 + c;
+            uint4 a = make_uint4(0, 0, 0, 0), w = a, u = a;
+            if (pieces && gk < K) {
+                if (src >= 0) a = *reinterpret_cast<const uint4*>(A + (size_t)src * K + gk);
+                if (gn < N) {
+                    w = *reinterpret_cast<const uint4*>(We + (size_t)gn * K + gk);
+                    if (GATED) u = *reinterpret_cast<const uint4*>(We + (size_t)(N + gn) * K + gk);
+                }
+                *reinterpret_cast<uint4*>(&As[r][c]) = a;
+                *reinterpret_cast<uint4*>(&Ws[r][c]) = w;
+                if (GATED) *reinterpret_cast<uint4*>(&Us[r][c]) = u;
+            } else {
+                for (int x = 0; x < 8; ++x) {
+                    const bool in = gk + x < K;
+                    As[r][c + x] = (in && src >= 0) ? A[(size_t)src * K + gk + x] : zero;
+                    Ws[r][c + x] = (in && gn < N) ? We[(size_t)gn * K + gk + x] : zero;
+                    if (GATED) Us[r][c + x] = (in && gn < N) ? We[(size_t)(N + gn) * K + gk + x] : zero;
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TBK; kk += 16) {
+            wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fa[2];
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fb[2], fu[GATED ? 2 : 1];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) wmma::load_matrix_sync(fa[i], &As[wm * 32 + i * 16][kk], TLD);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                wmma::load_matrix_sync(fb[j], &Ws[wn * 32 + j * 16][kk], TLD);
+                if (GATED) wmma::load_matrix_sync(fu[j], &Us[wn * 32 + j * 16][kk], TLD);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    wmma::mma_sync(acc[i][j], fa[i], fb[j], acc[i][j]);
+                    if (GATED) wmma::mma_sync(acu[i][j], fa[i], fu[j], acu[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            wmma::store_matrix_sync(&stage[warp][0][0][0], acc[i][j], 20, wmma::mem_row_major);
+            if (GATED) wmma::store_matrix_sync(&stage[warp][GATED ? 1 : 0][0][0], acu[i][j], 20, wmma::mem_row_major);
+            __syncwarp();
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const int el = lane + 32 * s;
+                const int rr = el >> 4, cc = el & 15;
+                const int r = wm * 32 + i * 16 + rr, gn = n0 + wn * 32 + j * 16 + cc;
+                if (r < rows && gn < N) {
+                    const size_t at = (size_t)(row0 + r) * N + gn;
+                    const float g = stage[warp][0][rr][cc];
+                    if (GATED) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(g / (1.f + expf(-g)) * stage[warp][GATED ? 1 : 0][rr][cc]);
+                    else reinterpret_cast<float*>(out)[at] = g;
+                }
+            }
+            __syncwarp();
+        }
+}
+
 // out[t] = sum_c weights[t][c] * y[row_of_pair[t top + c]] (+ shared[t])
 template <typename T>
 __global__ void routed_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair,
@@ -221,7 +421,7 @@ __global__ void routed_combine_kernel(const float* __restrict__ y, const int* __
 
 extern "C" long long fe_routed_experts_workspace(int T, int top, int experts, int D, int F, int dtype) {
     const long long pairs = (long long)T * top;
-    const long long tiles = (pairs + BM - 1) / BM + experts;
+    const long long tiles = (pairs + FEW_ROWS - 1) / FEW_ROWS + experts;      // the most tiles either form of the products makes
     const long long ints = (experts + 1) + 2 * pairs + 1 + 2 * tiles;
     const long long width = dtype == FE_F32 ? 4 : 2;
     return ((ints * 4 + 255) / 256 + (pairs * F * width + 255) / 256 + (pairs * D * 4 + 255) / 256) * 256;
@@ -237,39 +437,62 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
     FE_REQUIRE(workspace_bytes >= fe_routed_experts_workspace(T, top, experts, D, F, dtype), "routed_experts: workspace too small");
     const long long pairs = (long long)T * top;
     const int max_tiles = (int)((pairs + BM - 1) / BM + experts);
+    const long long most_tiles = (pairs + FEW_ROWS - 1) / FEW_ROWS + experts;
     FE_REQUIRE(max_tiles <= 65535, "routed_experts: too many rows in one step (%lld pairs)", pairs);
     int* offsets = (int*)workspace;
     int* row_of_pair = offsets + experts + 1;
     int* pair_of_row = row_of_pair + pairs;
     int* tiles = pair_of_row + pairs;
     int* tile_expert = tiles + 1;
-    int* tile_row0 = tile_expert + max_tiles;
-    const long long ints = (experts + 1) + 2 * pairs + 1 + 2 * (long long)max_tiles;
+    int* tile_row0 = tile_expert + most_tiles;
+    const long long ints = (experts + 1) + 2 * pairs + 1 + 2 * most_tiles;
     char* act = (char*)workspace + (ints * 4 + 255) / 256 * 256;
     const long long width = dtype == FE_F32 ? 4 : 2;
     float* y = (float*)(act + (pairs * F * width + 255) / 256 * 256);
-    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, (int)pairs, experts, BM, offsets, row_of_pair, pair_of_row, tiles,
-               tile_expert, tile_row0, status);
-    const dim3 grid1((F + BN - 1) / BN, max_tiles), grid2((D + BN - 1) / BN, max_tiles);
     const int threads = D >= 1024 ? 256 : 128;
-    if (dtype == FE_F32) {
-        fe::launch(routed_product_kernel<float, true>, grid1, 256, 0, stream, (const float*)h, (const int*)pair_of_row, top,
-                   (const float*)gate_up, (void*)act, (const int*)offsets, (const int*)tiles, (const int*)tile_expert,
-                   (const int*)tile_row0, F, D);
-        fe::launch(routed_product_kernel<float, false>, grid2, 256, 0, stream, (const float*)act, (const int*)nullptr, top,
-                   (const float*)down, (void*)y, (const int*)offsets, (const int*)tiles, (const int*)tile_expert,
-                   (const int*)tile_row0, D, F);
+    const long long width_bytes = dtype == FE_F32 ? 4 : 2;
+    const size_t few_smem1 = (size_t)FEW_ROWS * D * width_bytes, few_smem2 = (size_t)FEW_ROWS * F * width_bytes;
+    const bool few = pairs <= 64 && few_smem1 <= 160 * 1024 && few_smem2 <= 160 * 1024;
+    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, (int)pairs, experts, few ? FEW_ROWS : BM, offsets, row_of_pair, pair_of_row,
+               tiles, tile_expert, tile_row0, status);
+    const int* c_pairs = pair_of_row;
+    const int* c_none = nullptr;
+    const int *c_offsets = offsets, *c_tiles = tiles, *c_expert = tile_expert, *c_row0 = tile_row0;
+#define FE_ROUTED_PRODUCTS(KERNEL1, KERNEL2, TYPE, GRID1, GRID2, THREADS, SMEM1, SMEM2)                                                   \
+    fe::launch(KERNEL1, GRID1, THREADS, SMEM1, stream, (const TYPE*)h, c_pairs, top, (const TYPE*)gate_up, (void*)act, c_offsets, c_tiles, \
+               c_expert, c_row0, F, D);                                                                                                   \
+    fe::launch(KERNEL2, GRID2, THREADS, SMEM2, stream, (const TYPE*)act, c_none, top, (const TYPE*)down, (void*)y, c_offsets, c_tiles,    \
+               c_expert, c_row0, D, F)
+    if (few) {
+        const int few_tiles = (int)((pairs + FEW_ROWS - 1) / FEW_ROWS + experts);
+        const int per_block = FEW_WARPS * FEW_COLS;
+        const dim3 g1((F + per_block - 1) / per_block, few_tiles), g2((D + per_block - 1) / per_block, few_tiles);
+        cudaError_t err = cudaSuccess;
+        if (dtype == FE_F32) {
+            if (few_smem1 > 48 * 1024) err = cudaFuncSetAttribute(routed_product_few_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem1);
+            if (err == cudaSuccess && few_smem2 > 48 * 1024) err = cudaFuncSetAttribute(routed_product_few_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem2);
+            FE_REQUIRE(err == cudaSuccess, "routed_experts: %s", cudaGetErrorString(err));
+            FE_ROUTED_PRODUCTS((routed_product_few_kernel<float, true>), (routed_product_few_kernel<float, false>), float, g1, g2, FEW_WARPS * 32, few_smem1, few_smem2);
+        } else {
+            if (few_smem1 > 48 * 1024) err = cudaFuncSetAttribute(routed_product_few_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem1);
+            if (err == cudaSuccess && few_smem2 > 48 * 1024) err = cudaFuncSetAttribute(routed_product_few_kernel<bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem2);
+            FE_REQUIRE(err == cudaSuccess, "routed_experts: %s", cudaGetErrorString(err));
+            FE_ROUTED_PRODUCTS((routed_product_few_kernel<bf16, true>), (routed_product_few_kernel<bf16, false>), bf16, g1, g2, FEW_WARPS * 32, few_smem1, few_smem2);
+        }
+    } else {
+        const dim3 grid1((F + BN - 1) / BN, max_tiles), grid2((D + BN - 1) / BN, max_tiles);
+        if (dtype == FE_F32) {
+            FE_ROUTED_PRODUCTS((routed_product_kernel<float, true>), (routed_product_kernel<float, false>), float, grid1, grid2, 256, 0, 0);
+        } else {
+            FE_ROUTED_PRODUCTS((routed_product_mma_kernel<true>), (routed_product_mma_kernel<false>), bf16, grid1, grid2, 128, 0, 0);
+        }
+    }
+#undef FE_ROUTED_PRODUCTS
+    if (dtype == FE_F32)
         fe::launch(routed_combine_kernel<float>, T, threads, 0, stream, (const float*)y, (const int*)row_of_pair, weights,
                    (const float*)shared, (float*)out, top, D);
-    } else {
-        fe::launch(routed_product_kernel<bf16, true>, grid1, 256, 0, stream, (const bf16*)h, (const int*)pair_of_row, top,
-                   (const bf16*)gate_up, (void*)act, (const int*)offsets, (const int*)tiles, (const int*)tile_expert,
-                   (const int*)tile_row0, F, D);
-        fe::launch(routed_product_kernel<bf16, false>, grid2, 256, 0, stream, (const bf16*)act, (const int*)nullptr, top,
-                   (const bf16*)down, (void*)y, (const int*)offsets, (const int*)tiles, (const int*)tile_expert,
-                   (const int*)tile_row0, D, F);
+    else
         fe::launch(routed_combine_kernel<bf16>, T, threads, 0, stream, (const float*)y, (const int*)row_of_pair, weights,
                    (const bf16*)shared, (bf16*)out, top, D);
-    }
     return fe_check_launch("routed_experts");
 }

@@ -66,112 +66,187 @@ extern "C" int fe_token_shift_blend(const void* h, const float* mu, float* state
 }
 
 // ---------------------------------------------------------------------------------------------
-// The recurrence.  One block per (request, head); thread j owns value channel j and the state column S[.][j]: in
-// registers when the head size is one the kernel is compiled for (DH > 0), else in shared memory.  Tokens are walked
-// in tiles of TILE: the block stages r, k, the decay and v of a tile in shared memory, then every thread walks the
-// tile's tokens over all key channels.  A seat below 0 (a padding request) starts from zero and keeps nothing.
-constexpr int WKV_TILE = 16;
+// The recurrence.  The value channels of a head do not depend on one another, so a block owns a slice of them: one
+// block per (request, head, slice), a warp per 8 value channels of the slice.  The lanes of a warp are 8 groups of key
+// channels x 4 pairs of value channels; a thread keeps IPT key channels x 2 value channels of the state in registers
+// (head size <= 8 IPT; channels beyond the head size are zeros that change nothing).  Tokens are walked in tiles of
+// WKV_TILE: r, k and the decay of all key channels and v of the slice lie in shared memory, the next tile's values are
+// already on their way from global memory into registers while this one is walked, and the eight partial sums of an
+// output meet through three shuffles.  How many slices a head is cut into is chosen so that the blocks about fill the
+// device (a prompt of one request) or is one (a decode step of many requests).  A seat below 0 (a padding request)
+// starts from zero and keeps nothing.
+constexpr int WKV_TILE = 8;
+constexpr int WKV_GROUPS = 8;
 
-template <typename T, int DH>
-__global__ void wkv_recurrence_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
+template <typename T, int IPT, int PER>
+__global__ void __launch_bounds__(512) wkv_recurrence_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                                       const float* __restrict__ logits, const float* __restrict__ w0,
                                       const float* __restrict__ u, float* state, long long state_stride,
                                       const int* __restrict__ seats, const int* __restrict__ cu_q, float* __restrict__ out,
-                                      int heads, int d_runtime, int n_seats) {
+                                      int heads, int d, int n_seats) {
     griddep_wait();
     griddep_launch_dependents();
-    const int d = DH > 0 ? DH : d_runtime;
-    extern __shared__ float smem[];
-    float* rs = smem;                         // [TILE][d]
-    float* ks = rs + WKV_TILE * d;
-    float* ws = ks + WKV_TILE * d;
-    float* vs = ws + WKV_TILE * d;
-    float* us = vs + WKV_TILE * d;            // [d]
-    float* bs = us + d;                       // [d]  w0 of this head
-    float* column = bs + d;                   // [d][d] when DH == 0
+    constexpr int GP = IPT + 4;                   // a group's stretch in shared memory, padded against bank conflicts
+    constexpr int ROW = WKV_GROUPS * GP;
+    extern __shared__ __align__(16) float smem[];
+    float* rs = smem;                             // [TILE][ROW]
+    float* ks = rs + WKV_TILE * ROW;
+    float* ws = ks + WKV_TILE * ROW;
+    float* vs = ws + WKV_TILE * ROW;              // [TILE][columns of this block]
     const int req = blockIdx.x, head = blockIdx.y;
-    const int j = threadIdx.x;
-    const bool owner = j < d;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int columns = (blockDim.x >> 5) * 8;    // value channels of this block
+    const int j0 = blockIdx.z * columns;
+    const int group = lane >> 2;
+    const int local = warp * 8 + (lane & 3) * 2;  // this thread's two value channels within the block's slice
+    const int j = j0 + local;
+    const bool own0 = j < d, own1 = j + 1 < d;
     const int seat = seats[req];
     const bool seated = seat >= 0 && seat < n_seats;
     float* mine = seated ? state + (size_t)seat * state_stride + (size_t)head * d * d : nullptr;
     const int inner = heads * d;
-    float S[DH > 0 ? DH : 1];
-    if (owner) {
-        if (DH > 0) {
+    float S0[IPT], S1[IPT], bonus[IPT];
 #pragma unroll
-            for (int i = 0; i < (DH > 0 ? DH : 1); ++i) S[i] = mine ? mine[(size_t)i * d + j] : 0.f;
-        } else {
-            for (int i = 0; i < d; ++i) column[i * d + j] = mine ? mine[(size_t)i * d + j] : 0.f;
-        }
+    for (int x = 0; x < IPT; ++x) {
+        const int i = group * IPT + x;
+        S0[x] = (own0 && i < d && mine) ? mine[(size_t)i * d + j] : 0.f;
+        S1[x] = (own1 && i < d && mine) ? mine[(size_t)i * d + j + 1] : 0.f;
+        bonus[x] = i < d ? u[head * d + i] : 0.f;
     }
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        us[i] = u[head * d + i];
-        bs[i] = w0[head * d + i];
-    }
-    __syncthreads();
+    for (int e = threadIdx.x; e < 3 * WKV_TILE * ROW + WKV_TILE * columns; e += blockDim.x) smem[e] = 0.f;
     const int begin = cu_q[req], end = cu_q[req + 1];
-    for (int t0 = begin; t0 < end; t0 += WKV_TILE) {
-        const int count = min(WKV_TILE, end - t0);
-        for (int e = threadIdx.x; e < count * d; e += blockDim.x) {
-            const int tt = e / d, i = e % d;
-            const size_t at = (size_t)(t0 + tt) * inner + (size_t)head * d + i;
-            rs[e] = to_float(r[at]);
-            ks[e] = to_float(k[at]);
-            vs[e] = to_float(v[at]);
-            ws[e] = expf(-expf(logits[at] + bs[i]));
-        }
-        __syncthreads();
-        if (owner) {
-            for (int tt = 0; tt < count; ++tt) {
-                const float vj = vs[tt * d + j];
-                const float* rt = rs + tt * d;
-                const float* kt = ks + tt * d;
-                const float* wt = ws + tt * d;
-                float acc = 0.f;
-                if (DH > 0) {
+    // what a thread stages of a tile: elements e = threadIdx.x + n blockDim.x of [TILE][d] (r, k, decay) and of
+    // [TILE][columns] (v).  Where they lie does not depend on the tile, so it is worked out once; the loads of a tile are
+    // unconditional (an element beyond the tile's end reads the tile's first token again) and nothing is done with
+    // what they bring until the tile is staged, so that all of them are in flight together while the tile before is walked.
+    constexpr int PV = (PER + 3) / 4 + 1;
+    int from[PER], to[PER], token[PER], vfrom[PV], vtoken[PV];
+    float base[PER];
+    T raw_r[PER], raw_k[PER], raw_v[PV];
+    float raw_w[PER];
 #pragma unroll
-                    for (int i = 0; i < (DH > 0 ? DH : 1); ++i) {
-                        const float kv = kt[i] * vj;
-                        acc = fmaf(rt[i], fmaf(us[i], kv, S[i]), acc);
-                        S[i] = fmaf(wt[i], S[i], kv);
-                    }
-                } else {
-                    for (int i = 0; i < d; ++i) {
-                        const float kv = kt[i] * vj;
-                        const float s = column[i * d + j];
-                        acc = fmaf(rt[i], fmaf(us[i], kv, s), acc);
-                        column[i * d + j] = fmaf(wt[i], s, kv);
-                    }
-                }
-                out[(size_t)(t0 + tt) * inner + (size_t)head * d + j] = acc;
+    for (int n = 0; n < PER; ++n) {
+        const int e = threadIdx.x + n * blockDim.x;
+        const int tt = e / d, i = e - tt * d;
+        token[n] = tt < WKV_TILE ? tt : WKV_TILE;                  // WKV_TILE: never staged
+        from[n] = tt < WKV_TILE ? tt * inner + i : 0;
+        to[n] = tt * ROW + (i / IPT) * GP + i % IPT;
+        base[n] = w0[head * d + i];
+    }
+#pragma unroll
+    for (int n = 0; n < PV; ++n) {
+        const int e = threadIdx.x + n * blockDim.x;
+        const int tt = e / columns, c = e - tt * columns;
+        const bool real = tt < WKV_TILE && j0 + c < d;
+        vtoken[n] = real ? tt : WKV_TILE;
+        vfrom[n] = real ? tt * inner + j0 + c : 0;
+    }
+    auto fetch = [&](int t0) {
+        const int count = min(WKV_TILE, end - t0);
+        const size_t origin = (size_t)t0 * inner + (size_t)head * d;
+#pragma unroll
+        for (int n = 0; n < PER; ++n) {
+            const size_t at = origin + (token[n] < count ? from[n] : 0);
+            raw_r[n] = r[at];
+            raw_k[n] = k[at];
+            raw_w[n] = logits[at];
+        }
+#pragma unroll
+        for (int n = 0; n < PV; ++n) raw_v[n] = v[origin + (vtoken[n] < count ? vfrom[n] : 0)];
+    };
+    auto stage = [&](int t0) {
+        const int count = min(WKV_TILE, end - t0);
+#pragma unroll
+        for (int n = 0; n < PER; ++n) {
+            if (token[n] < count) {
+                rs[to[n]] = to_float(raw_r[n]);
+                ks[to[n]] = to_float(raw_k[n]);
+                ws[to[n]] = expf(-expf(raw_w[n] + base[n]));
             }
         }
-        __syncthreads();
-    }
-    if (owner && mine) {
-        if (DH > 0) {
 #pragma unroll
-            for (int i = 0; i < (DH > 0 ? DH : 1); ++i) mine[(size_t)i * d + j] = S[i];
-        } else {
-            for (int i = 0; i < d; ++i) mine[(size_t)i * d + j] = column[i * d + j];
+        for (int n = 0; n < PV; ++n) {
+            const int e = threadIdx.x + n * blockDim.x;
+            if (vtoken[n] < count) vs[e] = to_float(raw_v[n]);
+        }
+    };
+    if (begin < end) fetch(begin);
+    __syncthreads();                              // the zeros are written
+    for (int t0 = begin; t0 < end; t0 += WKV_TILE) {
+        const int count = min(WKV_TILE, end - t0);
+        stage(t0);
+        __syncthreads();
+        if (t0 + WKV_TILE < end) fetch(t0 + WKV_TILE);
+        for (int tt = 0; tt < count; ++tt) {
+            const float2 vj = *reinterpret_cast<const float2*>(vs + tt * columns + local);
+            const float* rt = rs + tt * ROW + group * GP;
+            const float* kt = ks + tt * ROW + group * GP;
+            const float* wt = ws + tt * ROW + group * GP;
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int x = 0; x < IPT; x += 4) {
+                const float4 r4 = *reinterpret_cast<const float4*>(rt + x);
+                const float4 k4 = *reinterpret_cast<const float4*>(kt + x);
+                const float4 w4 = *reinterpret_cast<const float4*>(wt + x);
+                const float rr[4] = {r4.x, r4.y, r4.z, r4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int y = 0; y < 4; ++y) {
+                    const float kv0 = kk[y] * vj.x, kv1 = kk[y] * vj.y;
+                    acc0 = fmaf(rr[y], fmaf(bonus[x + y], kv0, S0[x + y]), acc0);
+                    acc1 = fmaf(rr[y], fmaf(bonus[x + y], kv1, S1[x + y]), acc1);
+                    S0[x + y] = fmaf(ww[y], S0[x + y], kv0);
+                    S1[x + y] = fmaf(ww[y], S1[x + y], kv1);
+                }
+            }
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+                acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
+                acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
+            }
+            if (group == 0) {
+                float* o = out + (size_t)(t0 + tt) * inner + (size_t)head * d + j;
+                if (own0) o[0] = acc0;
+                if (own1) o[1] = acc1;
+            }
+        }
+        __syncthreads();                          // everyone is done with this tile before the next one is staged
+    }
+    if (mine) {
+#pragma unroll
+        for (int x = 0; x < IPT; ++x) {
+            const int i = group * IPT + x;
+            if (i < d && own0) mine[(size_t)i * d + j] = S0[x];
+            if (i < d && own1) mine[(size_t)i * d + j + 1] = S1[x];
         }
     }
 }
 
-template <typename T, int DH>
+template <typename T, int IPT>
 static int launch_wkv(const void* r, const void* k, const void* v, const float* logits, const float* w0, const float* u,
                       float* state, long long state_stride, const int* seats, const int* cu_q, float* out, int requests,
                       int heads, int d, int n_seats, cudaStream_t stream) {
-    const int threads = (d + 31) / 32 * 32;
-    size_t smem = ((size_t)4 * WKV_TILE * d + 2 * d) * sizeof(float);
-    if (DH == 0) smem += (size_t)d * d * sizeof(float);
-    if (smem > 48 * 1024) {
-        cudaError_t err = cudaFuncSetAttribute(wkv_recurrence_kernel<T, DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        FE_REQUIRE(err == cudaSuccess, "wkv_recurrence: %s", cudaGetErrorString(err));
-    }
-    fe::launch(wkv_recurrence_kernel<T, DH>, dim3(requests, heads), threads, smem, stream, (const T*)r, (const T*)k, (const T*)v,
-               logits, w0, u, state, state_stride, seats, cu_q, out, heads, d, n_seats);
+    // a warp per 8 value channels; a head is cut into slices until the blocks about fill the device twice, but a block
+    // keeps four warps at least: every block stages r, k and the decay of all key channels for itself (measured at 32
+    // heads of 64 and one prompt of 2,048 tokens: one warp a block 1.36 ms, two 0.84, four 0.47, eight 0.84)
+    const int head_warps = (d + 7) / 8;
+    const long long units = (long long)requests * heads;
+    const int most = head_warps / 4 > 1 ? head_warps / 4 : 1;
+    int slices = (int)((2LL * fe_sm_count() + units - 1) / units);
+    slices = slices < 1 ? 1 : (slices > most ? most : slices);
+    int warps = (head_warps + slices - 1) / slices;
+    slices = (head_warps + warps - 1) / warps;
+    // a thread stages at most PER elements of r, k and the decay of a tile: TILE x d over 32 x warps threads
+    const int need = (WKV_TILE * d + warps * 32 - 1) / (warps * 32);
+    const size_t smem = ((size_t)3 * WKV_TILE * WKV_GROUPS * (IPT + 4) + (size_t)WKV_TILE * warps * 8) * sizeof(float);
+#define FE_WKV_LAUNCH(PER)                                                                                                        \
+    fe::launch(wkv_recurrence_kernel<T, IPT, PER>, dim3(requests, heads, slices), warps * 32, smem, stream, (const T*)r, (const T*)k, \
+               (const T*)v, logits, w0, u, state, state_stride, seats, cu_q, out, heads, d, n_seats)
+    if (need <= 2) FE_WKV_LAUNCH(2);
+    else if (need <= 4) FE_WKV_LAUNCH(4);
+    else if (need <= 8) FE_WKV_LAUNCH(8);
+    else if (need <= 16) FE_WKV_LAUNCH(16);
+    else FE_WKV_LAUNCH(32);
+#undef FE_WKV_LAUNCH
     return fe_check_launch("wkv_recurrence");
 }
 
@@ -179,22 +254,19 @@ template <typename T>
 static int dispatch_wkv(const void* r, const void* k, const void* v, const float* logits, const float* w0, const float* u,
                         float* state, long long state_stride, const int* seats, const int* cu_q, float* out, int requests,
                         int heads, int d, int n_seats, cudaStream_t stream) {
-#define FE_WKV(DH) return launch_wkv<T, DH>(r, k, v, logits, w0, u, state, state_stride, seats, cu_q, out, requests, heads, d, n_seats, stream)
-    switch (d) {
-        case 32: FE_WKV(32);
-        case 64: FE_WKV(64);
-        case 128: FE_WKV(128);
-        default: FE_WKV(0);
-    }
+#define FE_WKV(IPT) return launch_wkv<T, IPT>(r, k, v, logits, w0, u, state, state_stride, seats, cu_q, out, requests, heads, d, n_seats, stream)
+    if (d <= 32) FE_WKV(4);
+    if (d <= 64) FE_WKV(8);
+    FE_WKV(16);
 #undef FE_WKV
 }
 
 extern "C" int fe_wkv_recurrence(const void* r, const void* k, const void* v, const float* logits, const float* w0,
                                  const float* u, float* state, long long state_stride, const int* seats, const int* cu_q,
                                  float* out, int requests, int heads, int d, int n_seats, int dtype, cudaStream_t stream) {
-    FE_REQUIRE(requests >= 0 && heads > 0 && d > 0 && d <= 192 && n_seats >= 0 && (long long)heads * d * d <= state_stride,
-               "wkv_recurrence: bad sizes (heads %d, head size %d; head sizes up to 192)", heads, d);
-    FE_REQUIRE(heads <= 65535, "wkv_recurrence: too many heads (%d)", heads);
+    FE_REQUIRE(requests >= 0 && heads > 0 && d > 0 && d <= 128 && n_seats >= 0 && (long long)heads * d * d <= state_stride,
+               "wkv_recurrence: bad sizes (heads %d, head size %d; head sizes up to 128)", heads, d);
+    FE_REQUIRE(heads <= 65535 && requests <= 2147483647, "wkv_recurrence: too many heads (%d)", heads);
     if (requests == 0) return 0;
     if (dtype == FE_F32)
         return dispatch_wkv<float>(r, k, v, logits, w0, u, state, state_stride, seats, cu_q, out, requests, heads, d, n_seats, stream);

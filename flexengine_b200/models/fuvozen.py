@@ -48,7 +48,7 @@ def build_fuvozen_plan(cfg: FuvozenConfig, decay_ranks=None) -> ModelPlan:
         p = f"l{i}."
         m = layer.mixer
         if layer.type == "wkv":
-            rank = (decay_ranks or {}).get(i, max(8, m.heads * m.dim // 8))
+            rank = (decay_ranks or {}).get(i, min(64, max(8, m.heads * m.dim // 8)))
             mixer = PartSpec("wkv", {"hidden_size": D, "heads": m.heads, "dim": m.dim, "decay_rank": rank, "eps": cfg.norm_eps})
             inner = m.heads * m.dim
             key = ("wkv", m.heads, m.dim)
