@@ -9,7 +9,7 @@
 // order, the result for a query does not depend on how its request was cut into steps.
 //
 // This kernel serves the true 32-bit path for every shape, and bfloat16 for shapes the tensor
-// core kernels do not take.
+// core kernels do not take (head sizes beyond 256: the rows of a wide cached latent).
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -118,7 +118,9 @@ static int launch_simt(const void* q, long long q_stride, void* out, long long o
     if (d <= 32) FE_LAUNCH_SIMT(1);
     else if (d <= 64) FE_LAUNCH_SIMT(2);
     else if (d <= 128) FE_LAUNCH_SIMT(4);
-    else FE_LAUNCH_SIMT(8);
+    else if (d <= 256) FE_LAUNCH_SIMT(8);
+    else if (d <= 512) FE_LAUNCH_SIMT(16);
+    else FE_LAUNCH_SIMT(32);
 #undef FE_LAUNCH_SIMT
     return fe_check_launch("paged_attention_simt");
 }
@@ -129,7 +131,7 @@ extern "C" int fe_paged_attention_simt(const void* q, long long q_stride, void* 
                                        int nq, int nkv, int d, int ps, int num_pages, float scale, int window,
                                        int dtype, int* status, cudaStream_t stream) {
     FE_REQUIRE(T_tokens >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "paged_attention: bad head counts %d/%d", nq, nkv);
-    FE_REQUIRE(d >= 16 && d <= 256 && d % 16 == 0, "paged_attention: head size %d is not a multiple of 16 in [16, 256]", d);
+    FE_REQUIRE(d >= 16 && d <= 1024 && d % 16 == 0, "paged_attention: head size %d is not a multiple of 16 in [16, 1024]", d);
     FE_REQUIRE(ps > 0 && num_pages > 0 && window >= 0, "paged_attention: bad page size, page count or window");
     FE_REQUIRE(q_stride % 8 == 0, "paged_attention: query row stride %lld must be a multiple of 8 elements", q_stride);
     if (T_tokens == 0) return 0;

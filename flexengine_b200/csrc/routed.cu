@@ -250,20 +250,27 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
                     load8<T>(wg + k, w);
                     if (GATED) load8<T>(wu + k, u);
                 } else {
-#pragma unroll
-                    for (int x = 0; x < PIECE; ++x) {
-                        w[x] = to_float(wg[k + x]);
-                        if (GATED) u[x] = to_float(wu[k + x]);
+                    const float4 w4 = *reinterpret_cast<const float4*>(wg + k);
+                    w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
+                    if (GATED) {
+                        const float4 u4 = *reinterpret_cast<const float4*>(wu + k);
+                        u[0] = u4.x; u[1] = u4.y; u[2] = u4.z; u[3] = u4.w;
                     }
                 }
 #pragma unroll
                 for (int r = 0; r < FEW_ROWS; ++r) {
+                    if (r < rows) {                              // the same for the whole block
+                        if (sizeof(T) == 2) {
+                            load8<T>(rows_s + r * K + k, a);
+                        } else {
+                            const float4 a4 = *reinterpret_cast<const float4*>(rows_s + r * K + k);
+                            a[0] = a4.x; a[1] = a4.y; a[2] = a4.z; a[3] = a4.w;
+                        }
 #pragma unroll
-                    for (int x = 0; x < PIECE; ++x) a[x] = to_float(rows_s[r * K + k + x]);
-#pragma unroll
-                    for (int x = 0; x < PIECE; ++x) {
-                        acc[r] = fmaf(a[x], w[x], acc[r]);
-                        if (GATED) acu[r] = fmaf(a[x], u[x], acu[r]);
+                        for (int x = 0; x < PIECE; ++x) {
+                            acc[r] = fmaf(a[x], w[x], acc[r]);
+                            if (GATED) acu[r] = fmaf(a[x], u[x], acu[r]);
+                        }
                     }
                 }
             }
@@ -399,6 +406,128 @@ routed_product_mma_kernel(const bf16* __restrict__ A, const int* __restrict__ pa
         }
 }
 
+// The tensor-core products once more for K a multiple of 8 (rows start on 16-byte boundaries): tiles of 128 rows x 64
+// columns (and the 64 paired "up" columns), 8 warps of 32 x 32 outputs, and the operands of the next 32 of K on their way
+// into the other half of shared memory (cp.async, 16 bytes a copy, zero fill for rows and columns beyond the edge)
+// while the tensor cores work on this one.
+constexpr int PBM = 128, PBN = 64, PBK = 32, PLD = PBK + 8, PSTAGES = 2;
+constexpr int PIPE_STAGE_ELEMS = (PBM + 2 * PBN) * PLD;        // A, W and U of one stage
+constexpr int PIPE_SMEM_BYTES = PSTAGES * PIPE_STAGE_ELEMS * 2;
+
+__device__ __forceinline__ void copy16(void* dst, const void* src, bool real) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = real ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+routed_product_pipe_kernel(const bf16* __restrict__ A, const int* __restrict__ pair_of_row, int top, const bf16* __restrict__ W,
+                           void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
+                           const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int N, int K) {
+    using namespace nvcuda;
+    griddep_wait();
+    griddep_launch_dependents();
+    if ((int)blockIdx.y >= tiles[0]) return;
+    extern __shared__ __align__(128) unsigned char pipe_smem[];
+    bf16* stages = reinterpret_cast<bf16*>(pipe_smem);
+    __shared__ int source[PBM];
+    const int e = tile_expert[blockIdx.y], row0 = tile_row0[blockIdx.y];
+    const int rows = min(PBM, offsets[e + 1] - row0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp >> 1, wn = warp & 1;
+    const int n0 = blockIdx.x * PBN;
+    if (tid < PBM) source[tid] = tid < rows ? (pair_of_row ? pair_of_row[row0 + tid] / top : row0 + tid) : -1;
+    __syncthreads();
+    const bf16* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[2][2], acu[GATED ? 2 : 1][2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            wmma::fill_fragment(acc[i][j], 0.f);
+            if (GATED) wmma::fill_fragment(acu[i][j], 0.f);
+        }
+    auto load_stage = [&](int stage, int k0) {
+        bf16* As = stages + stage * PIPE_STAGE_ELEMS;
+        bf16* Ws = As + PBM * PLD;
+        bf16* Us = Ws + PBN * PLD;
+        // A: 128 rows x 4 pieces = 512 copies, two a thread; W and U: 64 rows x 4 pieces = 256 copies each, one a thread
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int piece = tid + i * 256;
+            const int r = piece >> 2, c = (piece & 3) * 8;
+            const int src = source[r];
+            const bool real = src >= 0 && k0 + c < K;
+            copy16(As + r * PLD + c, real ? A + (size_t)src * K + k0 + c : A, real);
+        }
+        {
+            const int r = tid >> 2, c = (tid & 3) * 8;
+            const bool real = n0 + r < N && k0 + c < K;
+            copy16(Ws + r * PLD + c, real ? We + (size_t)(n0 + r) * K + k0 + c : We, real);
+            if (GATED) copy16(Us + r * PLD + c, real ? We + (size_t)(N + n0 + r) * K + k0 + c : We, real);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int steps = (K + PBK - 1) / PBK;
+    load_stage(0, 0);
+    for (int step = 0; step < steps; ++step) {
+        if (step + 1 < steps) {
+            load_stage((step + 1) & 1, (step + 1) * PBK);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const bf16* As = stages + (step & 1) * PIPE_STAGE_ELEMS;
+        const bf16* Ws = As + PBM * PLD;
+        const bf16* Us = Ws + PBN * PLD;
+#pragma unroll
+        for (int kk = 0; kk < PBK; kk += 16) {
+            wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fa[2];
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fb[2], fu[GATED ? 2 : 1];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) wmma::load_matrix_sync(fa[i], As + (wm * 32 + i * 16) * PLD + kk, PLD);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                wmma::load_matrix_sync(fb[j], Ws + (wn * 32 + j * 16) * PLD + kk, PLD);
+                if (GATED) wmma::load_matrix_sync(fu[j], Us + (wn * 32 + j * 16) * PLD + kk, PLD);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    wmma::mma_sync(acc[i][j], fa[i], fb[j], acc[i][j]);
+                    if (GATED) wmma::mma_sync(acu[i][j], fa[i], fu[j], acu[i][j]);
+                }
+        }
+        __syncthreads();                          // this stage is free for the copies of the step after next
+    }
+    // the accumulators pass through shared memory (the pipeline's, which is idle now), a 16 x 16 piece a warp at a time
+    float* mine = reinterpret_cast<float*>(pipe_smem) + warp * 2 * 16 * 20;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            wmma::store_matrix_sync(mine, acc[i][j], 20, wmma::mem_row_major);
+            if (GATED) wmma::store_matrix_sync(mine + 16 * 20, acu[i][j], 20, wmma::mem_row_major);
+            __syncwarp();
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const int el = lane + 32 * s;
+                const int rr = el >> 4, cc = el & 15;
+                const int r = wm * 32 + i * 16 + rr, gn = n0 + wn * 32 + j * 16 + cc;
+                if (r < rows && gn < N) {
+                    const size_t at = (size_t)(row0 + r) * N + gn;
+                    const float g = mine[rr * 20 + cc];
+                    if (GATED) reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(g / (1.f + expf(-g)) * mine[16 * 20 + rr * 20 + cc]);
+                    else reinterpret_cast<float*>(out)[at] = g;
+                }
+            }
+            __syncwarp();
+        }
+}
+
 // out[t] = sum_c weights[t][c] * y[row_of_pair[t top + c]] (+ shared[t])
 template <typename T>
 __global__ void routed_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair,
@@ -453,8 +582,10 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
     const long long width_bytes = dtype == FE_F32 ? 4 : 2;
     const size_t few_smem1 = (size_t)FEW_ROWS * D * width_bytes, few_smem2 = (size_t)FEW_ROWS * F * width_bytes;
     const bool few = pairs <= 64 && few_smem1 <= 160 * 1024 && few_smem2 <= 160 * 1024;
-    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, (int)pairs, experts, few ? FEW_ROWS : BM, offsets, row_of_pair, pair_of_row,
-               tiles, tile_expert, tile_row0, status);
+    // tensor cores with 128-row tiles and pipelined copies when rows start on 16-byte boundaries in both products
+    const bool piped = !few && dtype == FE_BF16 && D % 8 == 0 && F % 8 == 0;
+    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, (int)pairs, experts, few ? FEW_ROWS : (piped ? PBM : BM), offsets, row_of_pair,
+               pair_of_row, tiles, tile_expert, tile_row0, status);
     const int* c_pairs = pair_of_row;
     const int* c_none = nullptr;
     const int *c_offsets = offsets, *c_tiles = tiles, *c_expert = tile_expert, *c_row0 = tile_row0;
@@ -483,6 +614,12 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
         const dim3 grid1((F + BN - 1) / BN, max_tiles), grid2((D + BN - 1) / BN, max_tiles);
         if (dtype == FE_F32) {
             FE_ROUTED_PRODUCTS((routed_product_kernel<float, true>), (routed_product_kernel<float, false>), float, grid1, grid2, 256, 0, 0);
+        } else if (piped) {
+            cudaError_t err = cudaFuncSetAttribute(routed_product_pipe_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM_BYTES);
+            if (err == cudaSuccess) err = cudaFuncSetAttribute(routed_product_pipe_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM_BYTES);
+            FE_REQUIRE(err == cudaSuccess, "routed_experts: %s", cudaGetErrorString(err));
+            const dim3 p1((F + PBN - 1) / PBN, max_tiles), p2((D + PBN - 1) / PBN, max_tiles);
+            FE_ROUTED_PRODUCTS((routed_product_pipe_kernel<true>), (routed_product_pipe_kernel<false>), bf16, p1, p2, 256, PIPE_SMEM_BYTES, PIPE_SMEM_BYTES);
         } else {
             FE_ROUTED_PRODUCTS((routed_product_mma_kernel<true>), (routed_product_mma_kernel<false>), bf16, grid1, grid2, 128, 0, 0);
         }

@@ -599,7 +599,7 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
     T = qkv.shape[0]
     if qkv.dtype != k_cache.dtype:
         raise TypeError("queries and cache differ in dtype")
-    if qkv.dtype == torch.float32:
+    if qkv.dtype == torch.float32 or d > 256:          # the tensor-core kernels take head sizes up to 256
         return paged_attention_simt(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start,
                                     ctx.token_request, T, nq, nkv, d, page_size, scale, window)
     requests = ctx.cu_q.numel() - 1

@@ -294,11 +294,13 @@ def test_dense_feed_forward_alone(device, dtype):
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
-@pytest.mark.parametrize("experts,top,shared", [(5, 2, 16), (3, 3, 0), (70, 1, 8)])
-def test_routed_feed_forward_alone(device, dtype, experts, top, shared):
+@pytest.mark.parametrize("experts,top,shared,D,F", [(5, 2, 16, 48, 24), (3, 3, 0, 48, 24), (70, 1, 8, 48, 24), (4, 2, 12, 44, 20),
+                                                     (6, 2, 0, 136, 72)])
+def test_routed_feed_forward_alone(device, dtype, experts, top, shared, D, F):
+    """Also widths that are no multiples of 8 (rows off 16-byte boundaries) and tiles with edges on every side."""
     torch.manual_seed(4)
     dt = getattr(torch, dtype)
-    D, F, T = 48, 24, 70
+    T = 70 if D < 100 else 300
     weights = {"router": torch.randn(experts, D)}
     names = {"router.weight": ["router"], "experts.gate_up.weight": [], "experts.down.weight": []}
     for e in range(experts):
@@ -408,7 +410,8 @@ def latent_mixer(D, m, weights, device, dt):
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
-@pytest.mark.parametrize("shape", [(3, 16, 8, 24, 40, 12), (1, 32, 16, 8, 20, 0), (4, 32, 32, 40, 96, 21), (5, 8, 4, 8, 12, 3)])
+@pytest.mark.parametrize("shape", [(3, 16, 8, 24, 40, 12), (1, 32, 16, 8, 20, 0), (4, 32, 32, 40, 96, 21), (5, 8, 4, 8, 12, 3),
+                                   (2, 16, 16, 24, 272, 9), (20, 16, 8, 8, 24, 14)])      # a row beyond 256; more heads than a decode group takes
 def test_latent_attention_alone(device, dtype, shape):
     dt = getattr(torch, dtype)
     D, T = 48, 41
