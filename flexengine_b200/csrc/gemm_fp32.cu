@@ -77,21 +77,39 @@ gemm_fp32_skinny_kernel(const float* __restrict__ A, const float* __restrict__ W
     const int tid = threadIdx.x;
     const int m = tid / SC, n = tid % SC;
     const int m0 = blockIdx.y * SR, n0 = blockIdx.x * SC;
-    float acc = 0.f;
-    for (int k0 = 0; k0 < K; k0 += SK) {
+    // the next chunk is on its way from global memory into registers while this one is multiplied
+    float next_a[(SR * SK) / 128], next_w[(SC * SK) / 128];
+    auto fetch = [&](int k0) {
 #pragma unroll
         for (int i = 0; i < (SR * SK) / 128; ++i) {
             const int idx = tid + i * 128;
             const int r = idx / SK, c = idx % SK;
-            As[r][c] = (m0 + r < M && k0 + c < K) ? A[(size_t)(m0 + r) * K + k0 + c] : 0.f;
+            const bool real = m0 + r < M && k0 + c < K;
+            next_a[i] = real ? A[(size_t)(m0 + r) * K + k0 + c] : 0.f;
         }
 #pragma unroll
         for (int i = 0; i < (SC * SK) / 128; ++i) {
             const int idx = tid + i * 128;
             const int r = idx / SK, c = idx % SK;
-            Ws[r][c] = (n0 + r < N && k0 + c < K) ? W[(size_t)(n0 + r) * K + k0 + c] : 0.f;
+            const bool real = n0 + r < N && k0 + c < K;
+            next_w[i] = real ? W[(size_t)(n0 + r) * K + k0 + c] : 0.f;
+        }
+    };
+    float acc = 0.f;
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += SK) {
+#pragma unroll
+        for (int i = 0; i < (SR * SK) / 128; ++i) {
+            const int idx = tid + i * 128;
+            As[idx / SK][idx % SK] = next_a[i];
+        }
+#pragma unroll
+        for (int i = 0; i < (SC * SK) / 128; ++i) {
+            const int idx = tid + i * 128;
+            Ws[idx / SK][idx % SK] = next_w[i];
         }
         __syncthreads();
+        if (k0 + SK < K) fetch(k0 + SK);
 #pragma unroll 16
         for (int k = 0; k < SK; ++k) acc = fmaf(As[m][k], Ws[n][k], acc);
         __syncthreads();

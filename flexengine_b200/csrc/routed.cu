@@ -231,9 +231,74 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const T* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
     constexpr int PIECE = 16 / sizeof(T);                       // elements of a 16-byte piece
-    const bool pieces = K % PIECE == 0;
+    const int nbase = (blockIdx.x * FEW_WARPS + warp) * FEW_COLS;
+    if (nbase >= N) return;
+    if (K % PIECE == 0) {
+        // the warp's columns side by side: every step has one 16-byte load per column (and paired "up" column) in flight
+        float acc[FEW_COLS][FEW_ROWS], acu[GATED ? FEW_COLS : 1][FEW_ROWS];
+#pragma unroll
+        for (int c = 0; c < FEW_COLS; ++c)
+#pragma unroll
+            for (int r = 0; r < FEW_ROWS; ++r) {
+                acc[c][r] = 0.f;
+                if (GATED) acu[c][r] = 0.f;
+            }
+        for (int k = lane * PIECE; k < K; k += 32 * PIECE) {
+            float w[FEW_COLS][8], u[GATED ? FEW_COLS : 1][8];
+#pragma unroll
+            for (int c = 0; c < FEW_COLS; ++c) {
+                const int n = min(nbase + c, N - 1);            // a column beyond the edge repeats the last one and is not written
+                const T* wg = We + (size_t)n * K + k;
+                const T* wu = We + (size_t)(N + n) * K + k;
+                if (sizeof(T) == 2) {
+                    load8<T>(wg, w[c]);
+                    if (GATED) load8<T>(wu, u[c]);
+                } else {
+                    const float4 w4 = *reinterpret_cast<const float4*>(wg);
+                    w[c][0] = w4.x; w[c][1] = w4.y; w[c][2] = w4.z; w[c][3] = w4.w;
+                    if (GATED) {
+                        const float4 u4 = *reinterpret_cast<const float4*>(wu);
+                        u[c][0] = u4.x; u[c][1] = u4.y; u[c][2] = u4.z; u[c][3] = u4.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < FEW_ROWS; ++r) {
+                if (r < rows) {                                  // the same for the whole block
+                    float a[8];
+                    if (sizeof(T) == 2) {
+                        load8<T>(rows_s + r * K + k, a);
+                    } else {
+                        const float4 a4 = *reinterpret_cast<const float4*>(rows_s + r * K + k);
+                        a[0] = a4.x; a[1] = a4.y; a[2] = a4.z; a[3] = a4.w;
+                    }
+#pragma unroll
+                    for (int c = 0; c < FEW_COLS; ++c)
+#pragma unroll
+                        for (int x = 0; x < PIECE; ++x) {
+                            acc[c][r] = fmaf(a[x], w[c][x], acc[c][r]);
+                            if (GATED) acu[c][r] = fmaf(a[x], u[c][x], acu[c][r]);
+                        }
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < FEW_COLS; ++c)
+#pragma unroll
+            for (int r = 0; r < FEW_ROWS; ++r) {
+                if (r >= rows) continue;
+                const float g = warp_sum(acc[c][r]);
+                const float u = GATED ? warp_sum(acu[c][r]) : 0.f;
+                if (lane == 0 && nbase + c < N) {
+                    const size_t at = (size_t)(row0 + r) * N + nbase + c;
+                    if (GATED) reinterpret_cast<T*>(out)[at] = from_float<T>(g / (1.f + expf(-g)) * u);
+                    else reinterpret_cast<float*>(out)[at] = g;
+                }
+            }
+        return;
+    }
     for (int c = 0; c < FEW_COLS; ++c) {
-        const int n = (blockIdx.x * FEW_WARPS + warp) * FEW_COLS + c;
+        const int n = nbase + c;
         if (n >= N) break;
         const T* wg = We + (size_t)n * K;
         const T* wu = We + (size_t)(N + n) * K;
@@ -243,47 +308,14 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
             acc[r] = 0.f;
             if (GATED) acu[r] = 0.f;
         }
-        if (pieces) {
-            for (int k = lane * PIECE; k < K; k += 32 * PIECE) {
-                float w[8], u[8], a[8];
-                if (sizeof(T) == 2) {
-                    load8<T>(wg + k, w);
-                    if (GATED) load8<T>(wu + k, u);
-                } else {
-                    const float4 w4 = *reinterpret_cast<const float4*>(wg + k);
-                    w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
-                    if (GATED) {
-                        const float4 u4 = *reinterpret_cast<const float4*>(wu + k);
-                        u[0] = u4.x; u[1] = u4.y; u[2] = u4.z; u[3] = u4.w;
-                    }
-                }
+        for (int k = lane; k < K; k += 32) {
+            const float w = to_float(wg[k]);
+            const float u = GATED ? to_float(wu[k]) : 0.f;
 #pragma unroll
-                for (int r = 0; r < FEW_ROWS; ++r) {
-                    if (r < rows) {                              // the same for the whole block
-                        if (sizeof(T) == 2) {
-                            load8<T>(rows_s + r * K + k, a);
-                        } else {
-                            const float4 a4 = *reinterpret_cast<const float4*>(rows_s + r * K + k);
-                            a[0] = a4.x; a[1] = a4.y; a[2] = a4.z; a[3] = a4.w;
-                        }
-#pragma unroll
-                        for (int x = 0; x < PIECE; ++x) {
-                            acc[r] = fmaf(a[x], w[x], acc[r]);
-                            if (GATED) acu[r] = fmaf(a[x], u[x], acu[r]);
-                        }
-                    }
-                }
-            }
-        } else {
-            for (int k = lane; k < K; k += 32) {
-                const float w = to_float(wg[k]);
-                const float u = GATED ? to_float(wu[k]) : 0.f;
-#pragma unroll
-                for (int r = 0; r < FEW_ROWS; ++r) {
-                    const float a = to_float(rows_s[r * K + k]);
-                    acc[r] = fmaf(a, w, acc[r]);
-                    if (GATED) acu[r] = fmaf(a, u, acu[r]);
-                }
+            for (int r = 0; r < FEW_ROWS; ++r) {
+                const float a = to_float(rows_s[r * K + k]);
+                acc[r] = fmaf(a, w, acc[r]);
+                if (GATED) acu[r] = fmaf(a, u, acu[r]);
             }
         }
 #pragma unroll

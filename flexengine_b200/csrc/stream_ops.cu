@@ -198,7 +198,21 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, 
         up = softplusf(params[0]);
         down = 0.5f + softplusf(params[1]);
     }
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long stride = (long long)gridDim.x * blockDim.x, first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (n % 8 == 0 && ((((size_t)x) | ((size_t)out)) & 31) == 0) {           // eight elements a thread and step
+        for (long long i = first * 8; i < n; i += stride * 8) {
+            float z[8];
+            load8<T>(x + i, z);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                if (kind == 0) z[e] = tanhf(z[e]);
+                else z[e] = z[e] > 0.f ? fmaf(up * z[e], z[e], 0.5f * z[e]) : fmaf(down, expm1f(z[e]) - z[e], 0.5f * z[e]);
+            }
+            store8<T>(out + i, z);
+        }
+        return;
+    }
+    for (long long i = first; i < n; i += stride) {
         const float z = to_float(x[i]);
         float y;
         if (kind == 0) y = tanhf(z);
@@ -212,8 +226,9 @@ extern "C" int fe_activation(const void* x, void* out, long long n, int kind, co
     FE_REQUIRE(n >= 0 && (kind == 0 || (kind == 1 && params != nullptr)), "activation: bad arguments (kind %d)", kind);
     if (n == 0) return 0;
     const int threads = 256;
-    const long long want = (n + threads - 1) / threads;
-    const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+    const long long want = (n / 8 + threads) / threads;
+    const long long most = (long long)fe_sm_count() * 16;
+    const unsigned blocks = (unsigned)(want < most ? (want > 0 ? want : 1) : most);
     if (dtype == FE_F32)
         fe::launch(activation_kernel<float>, blocks, threads, 0, stream, (const float*)x, (float*)out, n, kind, params);
     else if (dtype == FE_BF16)

@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(512) wkv_recurrence_kernel(const T* __restrict
         stage(t0);
         __syncthreads();
         if (t0 + WKV_TILE < end) fetch(t0 + WKV_TILE);
-        for (int tt = 0; tt < count; ++tt) {
+        auto walk = [&](int tt) {
             const float2 vj = *reinterpret_cast<const float2*>(vs + tt * columns + local);
             const float* rt = rs + tt * ROW + group * GP;
             const float* kt = ks + tt * ROW + group * GP;
@@ -208,6 +208,12 @@ __global__ void __launch_bounds__(512) wkv_recurrence_kernel(const T* __restrict
                 if (own0) o[0] = acc0;
                 if (own1) o[1] = acc1;
             }
+        };
+        if (count == WKV_TILE) {
+#pragma unroll
+            for (int tt = 0; tt < WKV_TILE; ++tt) walk(tt);       // unrolled: a token's shuffles overlap the next token's products
+        } else {
+            for (int tt = 0; tt < count; ++tt) walk(tt);
         }
         __syncthreads();                          // everyone is done with this tile before the next one is staged
     }
