@@ -72,8 +72,8 @@ gemm_fp32_skinny_kernel(const float* __restrict__ A, const float* __restrict__ W
                         float* __restrict__ C, int M, int N, int K) {
     fe::griddep_wait();
     fe::griddep_launch_dependents();
-    __shared__ float As[SR][SK];
-    __shared__ float Ws[SC][SK + 1];
+    __shared__ __align__(16) float As[SR][SK];
+    __shared__ __align__(16) float Ws[SC][SK + 4];
     const int tid = threadIdx.x;
     const int m = tid / SC, n = tid % SC;
     const int m0 = blockIdx.y * SR, n0 = blockIdx.x * SC;
@@ -110,8 +110,15 @@ gemm_fp32_skinny_kernel(const float* __restrict__ A, const float* __restrict__ W
         }
         __syncthreads();
         if (k0 + SK < K) fetch(k0 + SK);
-#pragma unroll 16
-        for (int k = 0; k < SK; ++k) acc = fmaf(As[m][k], Ws[n][k], acc);
+#pragma unroll
+        for (int k = 0; k < SK; k += 4) {           // four at a time from shared memory; the chain stays in ascending k
+            const float4 a = *reinterpret_cast<const float4*>(&As[m][k]);
+            const float4 w = *reinterpret_cast<const float4*>(&Ws[n][k]);
+            acc = fmaf(a.x, w.x, acc);
+            acc = fmaf(a.y, w.y, acc);
+            acc = fmaf(a.z, w.z, acc);
+            acc = fmaf(a.w, w.w, acc);
+        }
         __syncthreads();
     }
     if (m0 + m < M && n0 + n < N) C[(size_t)(m0 + m) * N + n0 + n] = acc + (bias ? bias[n0 + n] : 0.f);

@@ -201,12 +201,13 @@ routed_product_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_r
 }
 
 // The same products for a handful of rows (a decode step): bound by reading the experts' matrices once.  A tile is up
-// to 8 sorted rows of one expert; a block stages them in shared memory and its 8 warps take 4 output columns each,
+// to 8 sorted rows of one expert (4 where the experts have four rows or fewer on average: half the accumulators, so two
+// blocks share a multiprocessor and twice the loads are in flight); a block stages them in shared memory and its 8 warps take 4 output columns each,
 // one after the other: the lanes walk K in 16-byte pieces of the expert's row (and of the paired "up" row when
 // GATED), multiply with all rows, and add up over the warp.
-constexpr int FEW_ROWS = 8, FEW_WARPS = 8, FEW_COLS = 4;
+constexpr int FEW_ROWS = 8, FEW_ROWS_SMALL = 4, FEW_WARPS = 8, FEW_COLS = 4;
 
-template <typename T, bool GATED>
+template <typename T, bool GATED, int ROWS>
 __global__ void __launch_bounds__(FEW_WARPS * 32)
 routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_of_row, int top, const T* __restrict__ W,
                           void* __restrict__ out, const int* __restrict__ offsets, const int* __restrict__ tiles,
@@ -215,10 +216,10 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
     griddep_launch_dependents();
     if ((int)blockIdx.y >= tiles[0]) return;
     extern __shared__ __align__(16) unsigned char few_smem[];
-    T* rows_s = reinterpret_cast<T*>(few_smem);                 // [FEW_ROWS][K]
+    T* rows_s = reinterpret_cast<T*>(few_smem);                 // [ROWS][K]
     const int e = tile_expert[blockIdx.y], row0 = tile_row0[blockIdx.y];
-    const int rows = min(FEW_ROWS, offsets[e + 1] - row0);
-    for (int idx = threadIdx.x; idx < FEW_ROWS * K; idx += blockDim.x) {
+    const int rows = min(ROWS, offsets[e + 1] - row0);
+    for (int idx = threadIdx.x; idx < ROWS * K; idx += blockDim.x) {
         const int r = idx / K, k = idx % K;
         T v = from_float<T>(0.f);
         if (r < rows) {
@@ -235,11 +236,11 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
     if (nbase >= N) return;
     if (K % PIECE == 0) {
         // the warp's columns side by side: every step has one 16-byte load per column (and paired "up" column) in flight
-        float acc[FEW_COLS][FEW_ROWS], acu[GATED ? FEW_COLS : 1][FEW_ROWS];
+        float acc[FEW_COLS][ROWS], acu[GATED ? FEW_COLS : 1][ROWS];
 #pragma unroll
         for (int c = 0; c < FEW_COLS; ++c)
 #pragma unroll
-            for (int r = 0; r < FEW_ROWS; ++r) {
+            for (int r = 0; r < ROWS; ++r) {
                 acc[c][r] = 0.f;
                 if (GATED) acu[c][r] = 0.f;
             }
@@ -263,7 +264,7 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
                 }
             }
 #pragma unroll
-            for (int r = 0; r < FEW_ROWS; ++r) {
+            for (int r = 0; r < ROWS; ++r) {
                 if (r < rows) {                                  // the same for the whole block
                     float a[8];
                     if (sizeof(T) == 2) {
@@ -285,7 +286,7 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
 #pragma unroll
         for (int c = 0; c < FEW_COLS; ++c)
 #pragma unroll
-            for (int r = 0; r < FEW_ROWS; ++r) {
+            for (int r = 0; r < ROWS; ++r) {
                 if (r >= rows) continue;
                 const float g = warp_sum(acc[c][r]);
                 const float u = GATED ? warp_sum(acu[c][r]) : 0.f;
@@ -302,9 +303,9 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
         if (n >= N) break;
         const T* wg = We + (size_t)n * K;
         const T* wu = We + (size_t)(N + n) * K;
-        float acc[FEW_ROWS], acu[GATED ? FEW_ROWS : 1];
+        float acc[ROWS], acu[GATED ? ROWS : 1];
 #pragma unroll
-        for (int r = 0; r < FEW_ROWS; ++r) {
+        for (int r = 0; r < ROWS; ++r) {
             acc[r] = 0.f;
             if (GATED) acu[r] = 0.f;
         }
@@ -312,14 +313,14 @@ routed_product_few_kernel(const T* __restrict__ A, const int* __restrict__ pair_
             const float w = to_float(wg[k]);
             const float u = GATED ? to_float(wu[k]) : 0.f;
 #pragma unroll
-            for (int r = 0; r < FEW_ROWS; ++r) {
+            for (int r = 0; r < ROWS; ++r) {
                 const float a = to_float(rows_s[r * K + k]);
                 acc[r] = fmaf(a, w, acc[r]);
                 if (GATED) acu[r] = fmaf(a, u, acu[r]);
             }
         }
 #pragma unroll
-        for (int r = 0; r < FEW_ROWS; ++r) {
+        for (int r = 0; r < ROWS; ++r) {
             const float g = warp_sum(acc[r]);
             const float u = GATED ? warp_sum(acu[r]) : 0.f;
             if (lane == 0 && r < rows) {
@@ -568,7 +569,7 @@ __global__ void routed_combine_kernel(const float* __restrict__ y, const int* __
     griddep_wait();
     griddep_launch_dependents();
     const int t = blockIdx.x;
-    for (int j = threadIdx.x; j < D; j += blockDim.x) {
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < D; j += gridDim.y * blockDim.x) {
         float total = 0.f;
         for (int c = 0; c < top; ++c) {
             const int row = row_of_pair[(size_t)t * top + c];
@@ -582,7 +583,7 @@ __global__ void routed_combine_kernel(const float* __restrict__ y, const int* __
 
 extern "C" long long fe_routed_experts_workspace(int T, int top, int experts, int D, int F, int dtype) {
     const long long pairs = (long long)T * top;
-    const long long tiles = (pairs + FEW_ROWS - 1) / FEW_ROWS + experts;      // the most tiles either form of the products makes
+    const long long tiles = (pairs + FEW_ROWS_SMALL - 1) / FEW_ROWS_SMALL + experts;      // the most tiles any form of the products makes
     const long long ints = (experts + 1) + 2 * pairs + 1 + 2 * tiles;
     const long long width = dtype == FE_F32 ? 4 : 2;
     return ((ints * 4 + 255) / 256 + (pairs * F * width + 255) / 256 + (pairs * D * 4 + 255) / 256) * 256;
@@ -598,7 +599,7 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
     FE_REQUIRE(workspace_bytes >= fe_routed_experts_workspace(T, top, experts, D, F, dtype), "routed_experts: workspace too small");
     const long long pairs = (long long)T * top;
     const int max_tiles = (int)((pairs + BM - 1) / BM + experts);
-    const long long most_tiles = (pairs + FEW_ROWS - 1) / FEW_ROWS + experts;
+    const long long most_tiles = (pairs + FEW_ROWS_SMALL - 1) / FEW_ROWS_SMALL + experts;
     FE_REQUIRE(max_tiles <= 65535, "routed_experts: too many rows in one step (%lld pairs)", pairs);
     int* offsets = (int*)workspace;
     int* row_of_pair = offsets + experts + 1;
@@ -612,11 +613,12 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
     float* y = (float*)(act + (pairs * F * width + 255) / 256 * 256);
     const int threads = D >= 1024 ? 256 : 128;
     const long long width_bytes = dtype == FE_F32 ? 4 : 2;
-    const size_t few_smem1 = (size_t)FEW_ROWS * D * width_bytes, few_smem2 = (size_t)FEW_ROWS * F * width_bytes;
+    const int few_rows = pairs <= (long long)FEW_ROWS_SMALL * experts ? FEW_ROWS_SMALL : FEW_ROWS;
+    const size_t few_smem1 = (size_t)few_rows * D * width_bytes, few_smem2 = (size_t)few_rows * F * width_bytes;
     const bool few = pairs <= 64 && few_smem1 <= 160 * 1024 && few_smem2 <= 160 * 1024;
     // tensor cores with 128-row tiles and pipelined copies when rows start on 16-byte boundaries in both products
     const bool piped = !few && dtype == FE_BF16 && D % 8 == 0 && F % 8 == 0;
-    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, (int)pairs, experts, few ? FEW_ROWS : (piped ? PBM : BM), offsets, row_of_pair,
+    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, (int)pairs, experts, few ? few_rows : (piped ? PBM : BM), offsets, row_of_pair,
                pair_of_row, tiles, tile_expert, tile_row0, status);
     const int* c_pairs = pair_of_row;
     const int* c_none = nullptr;
@@ -627,21 +629,28 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
     fe::launch(KERNEL2, GRID2, THREADS, SMEM2, stream, (const TYPE*)act, c_none, top, (const TYPE*)down, (void*)y, c_offsets, c_tiles,    \
                c_expert, c_row0, D, F)
     if (few) {
-        const int few_tiles = (int)((pairs + FEW_ROWS - 1) / FEW_ROWS + experts);
+        const int few_tiles = (int)((pairs + few_rows - 1) / few_rows + experts);
         const int per_block = FEW_WARPS * FEW_COLS;
         const dim3 g1((F + per_block - 1) / per_block, few_tiles), g2((D + per_block - 1) / per_block, few_tiles);
-        cudaError_t err = cudaSuccess;
+#define FE_ROUTED_FEW(TYPE, ROWS)                                                                                                       \
+    do {                                                                                                                                \
+        cudaError_t err = cudaSuccess;                                                                                                  \
+        if (few_smem1 > 48 * 1024)                                                                                                      \
+            err = cudaFuncSetAttribute(routed_product_few_kernel<TYPE, true, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem1); \
+        if (err == cudaSuccess && few_smem2 > 48 * 1024)                                                                                \
+            err = cudaFuncSetAttribute(routed_product_few_kernel<TYPE, false, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem2); \
+        FE_REQUIRE(err == cudaSuccess, "routed_experts: %s", cudaGetErrorString(err));                                                  \
+        FE_ROUTED_PRODUCTS((routed_product_few_kernel<TYPE, true, ROWS>), (routed_product_few_kernel<TYPE, false, ROWS>), TYPE, g1, g2, \
+                           FEW_WARPS * 32, few_smem1, few_smem2);                                                                       \
+    } while (0)
         if (dtype == FE_F32) {
-            if (few_smem1 > 48 * 1024) err = cudaFuncSetAttribute(routed_product_few_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem1);
-            if (err == cudaSuccess && few_smem2 > 48 * 1024) err = cudaFuncSetAttribute(routed_product_few_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem2);
-            FE_REQUIRE(err == cudaSuccess, "routed_experts: %s", cudaGetErrorString(err));
-            FE_ROUTED_PRODUCTS((routed_product_few_kernel<float, true>), (routed_product_few_kernel<float, false>), float, g1, g2, FEW_WARPS * 32, few_smem1, few_smem2);
+            if (few_rows == FEW_ROWS_SMALL) FE_ROUTED_FEW(float, FEW_ROWS_SMALL);
+            else FE_ROUTED_FEW(float, FEW_ROWS);
         } else {
-            if (few_smem1 > 48 * 1024) err = cudaFuncSetAttribute(routed_product_few_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem1);
-            if (err == cudaSuccess && few_smem2 > 48 * 1024) err = cudaFuncSetAttribute(routed_product_few_kernel<bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem2);
-            FE_REQUIRE(err == cudaSuccess, "routed_experts: %s", cudaGetErrorString(err));
-            FE_ROUTED_PRODUCTS((routed_product_few_kernel<bf16, true>), (routed_product_few_kernel<bf16, false>), bf16, g1, g2, FEW_WARPS * 32, few_smem1, few_smem2);
+            if (few_rows == FEW_ROWS_SMALL) FE_ROUTED_FEW(bf16, FEW_ROWS_SMALL);
+            else FE_ROUTED_FEW(bf16, FEW_ROWS);
         }
+#undef FE_ROUTED_FEW
     } else {
         const dim3 grid1((F + BN - 1) / BN, max_tiles), grid2((D + BN - 1) / BN, max_tiles);
         if (dtype == FE_F32) {
@@ -657,11 +666,13 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
         }
     }
 #undef FE_ROUTED_PRODUCTS
+    const int stretches = T >= 512 ? 1 : (D + threads - 1) / threads;          // few tokens: one column a thread
+    const dim3 combine(T, stretches < 65535 ? stretches : 65535);
     if (dtype == FE_F32)
-        fe::launch(routed_combine_kernel<float>, T, threads, 0, stream, (const float*)y, (const int*)row_of_pair, weights,
+        fe::launch(routed_combine_kernel<float>, combine, threads, 0, stream, (const float*)y, (const int*)row_of_pair, weights,
                    (const float*)shared, (float*)out, top, D);
     else
-        fe::launch(routed_combine_kernel<bf16>, T, threads, 0, stream, (const float*)y, (const int*)row_of_pair, weights,
+        fe::launch(routed_combine_kernel<bf16>, combine, threads, 0, stream, (const float*)y, (const int*)row_of_pair, weights,
                    (const bf16*)shared, (bf16*)out, top, D);
     return fe_check_launch("routed_experts");
 }

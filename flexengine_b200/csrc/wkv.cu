@@ -12,7 +12,8 @@
 using namespace fe;
 
 // ---------------------------------------------------------------------------------------------
-// One block per token.  ``state`` rows are seats; the kept row of a seat (the last normalised input of the step before)
+// Blocks (token, stretch of columns): one column a thread in a step of few tokens, so that a handful of rows is still
+// a few dozen blocks.  ``state`` rows are seats; the kept row of a seat (the last normalised input of the step before)
 // starts at ``offset`` floats into its row.  The block of a request's first token reads the kept row and writes the
 // request's last row of this step in its place, element by element in the same thread, so nobody else touches it.
 template <typename T>
@@ -32,7 +33,7 @@ __global__ void token_shift_blend_kernel(const T* __restrict__ h, const float* _
     const T* prev = t > first ? h + (size_t)(t - 1) * D : nullptr;
     const T* last = h + (size_t)(cu_q[r + 1] - 1) * D;
     const size_t plane = (size_t)T_tokens * D;
-    for (int j = threadIdx.x; j < D; j += blockDim.x) {
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < D; j += gridDim.y * blockDim.x) {
         const float x = to_float(row[j]);
         float before;
         if (prev) before = to_float(prev[j]);
@@ -54,11 +55,13 @@ extern "C" int fe_token_shift_blend(const void* h, const float* mu, float* state
     FE_REQUIRE(T >= 0 && D > 0 && n_seats >= 0 && offset >= 0 && offset + D <= state_stride, "token_shift_blend: bad sizes");
     if (T == 0) return 0;
     const int threads = D >= 1024 ? 256 : 128;
+    const int stretches = T >= 512 ? 1 : (D + threads - 1) / threads;
+    const dim3 grid(T, stretches < 65535 ? stretches : 65535);
     if (dtype == FE_F32)
-        fe::launch(token_shift_blend_kernel<float>, T, threads, 0, stream, (const float*)h, mu, state, state_stride, offset, seats,
+        fe::launch(token_shift_blend_kernel<float>, grid, threads, 0, stream, (const float*)h, mu, state, state_stride, offset, seats,
                    cu_q, token_req, (float*)blends, blend_w, T, D, n_seats);
     else if (dtype == FE_BF16)
-        fe::launch(token_shift_blend_kernel<bf16>, T, threads, 0, stream, (const bf16*)h, mu, state, state_stride, offset, seats,
+        fe::launch(token_shift_blend_kernel<bf16>, grid, threads, 0, stream, (const bf16*)h, mu, state, state_stride, offset, seats,
                    cu_q, token_req, (bf16*)blends, blend_w, T, D, n_seats);
     else
         FE_REQUIRE(false, "token_shift_blend: unknown dtype %d", dtype);

@@ -493,6 +493,30 @@ def test_model_against_plain(model_dirs, name, kind, device, dtype):
         ops_for(device).check_status(device)
 
 
+STACKS = {
+    "only the recurrence": config(97, 48, 3, 1e-5, 31, (5, 3), [(wkv(2, 24), dense(64)), (wkv(3, 16), moe(4, 2, 16))]),
+    "only attention": config(97, 48, 1, 1e-5, 31, (5, 3), [(latent(2, 16, 8, 16, 24, 6), None), (latent(2, 16, 8, 16, 24, 6), dense(32))]),
+    "one layer": config(50, 32, 2, 1e-5, 7, (1, 1), [(wkv(1, 32), None)]),
+}
+
+
+@pytest.mark.parametrize("device,dtype", CASES)
+@pytest.mark.parametrize("stack", list(STACKS))
+def test_stacks_of_one_kind(tmp_path, stack, device, dtype):
+    """A model without paged groups, one without recurrent state, and one of a single layer without a feed-forward."""
+    cfg = STACKS[stack]
+    write_random_model(cfg, str(tmp_path), seed=3)
+    ids = helpers.random_prompt(random.Random(1), 45, cfg["vocab"])
+    runner = make_runner(str(tmp_path), dtype, device, 8, 8)
+    got = [runner.step([StepEntry("a", ids[:20], list(range(20)))]), runner.step([StepEntry("a", ids[20:44], list(range(24)))]),
+           runner.step([StepEntry("a", ids[44:], [0])])]
+    decided = []
+    want = plain_logits(str(tmp_path), ids, decided)
+    close(torch.cat([g.float().cpu() for g in got]), want, dtype, stack, rows=decided[0])
+    runner.finish("a")
+    runner.cache.assert_invariants()
+
+
 @pytest.mark.parametrize("device,dtype", CASES)
 def test_together_and_alone(model_dirs, device, dtype):
     """Unequal requests in one batch against each alone: the same logits (to rounding in bfloat16)."""
