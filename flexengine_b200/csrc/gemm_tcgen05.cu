@@ -8,11 +8,16 @@
 // allocation, warps 2..5 are the epilogue: each reads its quarter of the accumulator's lanes with
 // tcgen05.ld and writes the rows out.  The accumulator is double-buffered in TMEM (2 x 256
 // columns), so the epilogue of one tile runs under the MMAs of the next.  UMMA shape 128 x 256 x 16.
-//   plain epilogue:  a 128 x 256 output tile, bfloat16
+//   plain epilogue:  a 128 x 256 output tile, bfloat16 (or float, for a product whose results are added up afterwards)
 //   SwiGLU epilogue: W is [2I, K] (gate rows, then up rows); the block loads 128 gate rows and
 //                    their 128 up rows as one 256-row B tile, so accumulator columns j and 128 + j
 //                    belong to output column j: out = silu(gate) * up, a 128 x 128 tile of bfloat16 [M, I].
 // The reference runs these products through cuBLAS (inference/models/qwen2.py:99-101,129-130).
+//
+// Grouped form (a routed feed-forward): the rows of x are sorted by expert, W holds the experts' matrices one after the
+// other, and the tiles come from a list made on the device: (expert, first row) per row tile, their number in tiles[0].
+// A row tile may reach beyond its expert's rows and a column tile beyond its expert's columns: what lies beyond is
+// computed with the wrong operands and never written.  The grid is one block per SM whatever the list holds.
 //
 // Every wait on an mbarrier is bounded (about two seconds): when it runs out the thread records it
 // in the status word and raises a flag that makes every role leave its loop; all threads still
@@ -33,7 +38,7 @@ constexpr int STAGES = 4;
 constexpr int THREADS = 192;
 constexpr long long WAIT_LIMIT = 4000000000LL;      // clock cycles
 
-enum { EPI_BF16 = 0, EPI_SWIGLU = 2 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -143,8 +148,9 @@ constexpr int ACC_BUFFERS = 2;
 template <int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    bf16* __restrict__ out, int M, int N_out, int K, int up_row_offset, int m_tiles, int n_tiles,
-                    int* __restrict__ status) {
+                    void* __restrict__ out_raw, int M, int N_out, int K, int up_row_offset, int m_tiles, int n_tiles,
+                    const int* __restrict__ g_tiles, const int* __restrict__ g_expert, const int* __restrict__ g_row0,
+                    const int* __restrict__ g_offsets, int w_rows, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
     __shared__ __align__(8) unsigned long long acc_full[ACC_BUFFERS], acc_empty[ACC_BUFFERS];
@@ -159,7 +165,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     griddep_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BK - 1) / BK;
-    const int total_tiles = m_tiles * n_tiles;
+    const bool grouped = g_tiles != nullptr;
+    const int total_tiles = grouped ? g_tiles[0] * n_tiles : m_tiles * n_tiles;
+    // where tile t lies: first row and column, the first row of W of its expert, and the row its rows end before
+    auto origin = [&](int t, int& m0, int& n0, int& w0, int& row_end) {
+        if (grouped) {
+            const int entry = t / n_tiles;                 // column tiles fastest: blocks that run together share their rows of x
+            const int e = g_expert[entry];
+            m0 = g_row0[entry];
+            n0 = (t - entry * n_tiles) * OUT_COLS;
+            w0 = e * w_rows;
+            row_end = g_offsets[e + 1];
+        } else {
+            tile_origin(t, m_tiles, n_tiles, OUT_COLS, m0, n0);
+            w0 = 0;
+            row_end = M;
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -177,8 +199,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---- TMA producer ----
         int kbg = 0;                                   // k blocks issued so far, over all tiles
         for (int t = blockIdx.x; t < total_tiles && !give_up; t += gridDim.x) {
-            int m0, n0;
-            tile_origin(t, m_tiles, n_tiles, OUT_COLS, m0, n0);
+            int m0, n0, w0, row_end;
+            origin(t, m0, n0, w0, row_end);
             for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
                 const int s = kbg % STAGES, use = kbg / STAGES;
                 if (!mbar_wait(&empty_bar[s], (use & 1) ^ 1)) { give_up = 1; break; }   // parity 1 passes at once at the start
@@ -186,8 +208,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 unsigned char* b = a + A_BYTES;
                 mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
                 tma_load_2d(a, &map_a, kb * BK, m0, &full_bar[s]);
-                tma_load_2d(b, &map_b, kb * BK, n0, &full_bar[s]);                      // 128 rows of W (gate rows for SwiGLU)
-                tma_load_2d(b + 128 * BK * 2, &map_b, kb * BK, (EPI == EPI_SWIGLU ? up_row_offset + n0 : n0 + 128),
+                tma_load_2d(b, &map_b, kb * BK, w0 + n0, &full_bar[s]);                 // 128 rows of W (gate rows for SwiGLU)
+                tma_load_2d(b + 128 * BK * 2, &map_b, kb * BK, w0 + (EPI == EPI_SWIGLU ? up_row_offset + n0 : n0 + 128),
                             &full_bar[s]);                                              // the next 128 rows, or their up rows
             }
         }
@@ -221,8 +243,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int i = 0;
         for (int t = blockIdx.x; t < total_tiles && !give_up; t += gridDim.x, ++i) {
             const int buf = i & 1;
-            int m0, n0;
-            tile_origin(t, m_tiles, n_tiles, OUT_COLS, m0, n0);
+            int m0, n0, w0, row_end;
+            origin(t, m0, n0, w0, row_end);
             if (!mbar_wait(&acc_full[buf], (i >> 1) & 1)) { give_up = 1; break; }
             tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
@@ -237,8 +259,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = v[j] / (1.f + expf(-v[j])) * u[j];
                 }
-                if (row < M) {
-                    bf16* dst = out + (size_t)row * N_out + n0 + c;
+                if (row < row_end && EPI == EPI_F32) {
+                    float* dst = reinterpret_cast<float*>(out_raw) + (size_t)row * N_out + n0 + c;
+                    if (n0 + c + 32 <= N_out && (N_out & 3) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c + j < N_out) dst[j] = v[j];
+                    }
+                } else if (row < row_end) {
+                    bf16* dst = reinterpret_cast<bf16*>(out_raw) + (size_t)row * N_out + n0 + c;
                     if (n0 + c + 32 <= N_out && (N_out & 7) == 0) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) store8<bf16>(dst + j, v + j);
@@ -291,22 +322,25 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
     return 0;
 }
 
+// ``g_tiles`` null: one product, W is [N, K].  Else the grouped form: W is [w_rows_total, K], every expert owns N rows of it.
 template <int EPI>
-int launch(const void* x, const void* W, void* out, int M, int N, int K, int* status, cudaStream_t stream) {
+int launch(const void* x, const void* W, void* out, int M, int N, int K, int* status, cudaStream_t stream,
+           const int* g_tiles = nullptr, const int* g_expert = nullptr, const int* g_row0 = nullptr, const int* g_offsets = nullptr,
+           long long w_rows_total = 0) {
     const int n_out = EPI == EPI_SWIGLU ? N / 2 : N;
     constexpr int OUT_COLS = EPI == EPI_SWIGLU ? 128 : 256;
     CUtensorMap map_a, map_b;
     if (make_map(&map_a, x, M, K, BM)) return 1;
-    if (make_map(&map_b, W, N, K, 128)) return 1;
+    if (make_map(&map_b, W, g_tiles ? w_rows_total : N, K, 128)) return 1;
     const size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
     cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     FE_REQUIRE(err == cudaSuccess, "gemm_tcgen05: %s", cudaGetErrorString(err));
     const int sms = fe_sm_count();
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (n_out + OUT_COLS - 1) / OUT_COLS;
     const long long total = (long long)m_tiles * n_tiles;
-    const int blocks = (int)(total < sms ? total : sms);        // one persistent block per SM
-    fe::launch(gemm_tcgen05_kernel<EPI>, blocks, THREADS, smem, stream, map_a, map_b, (bf16*)out, M, n_out, K, n_out,
-               m_tiles, n_tiles, status);
+    const int blocks = g_tiles ? sms : (int)(total < sms ? total : sms);        // one persistent block per SM
+    fe::launch(gemm_tcgen05_kernel<EPI>, blocks, THREADS, smem, stream, map_a, map_b, out, M, n_out, K, n_out,
+               m_tiles, n_tiles, g_tiles, g_expert, g_row0, g_offsets, N, status);
     return fe_check_launch("gemm_tcgen05");
 }
 
@@ -324,4 +358,23 @@ extern "C" int fe_gemm_tcgen05(const void* x, const void* W, void* out, int M, i
         return launch<EPI_SWIGLU>(x, W, out, M, N, K, status, stream);
     }
     FE_REQUIRE(false, "gemm_tcgen05: unknown epilogue %d", epilogue);
+}
+
+// The grouped form: x [rows, K] sorted by expert, W [experts * N, K] (every expert's N rows; for SwiGLU its gate rows,
+// then its up rows), the row tiles of 128 from a list on the device (tiles[0] of them: tile_expert, tile_row0; offsets
+// [experts + 1] are the experts' row ranges).  epilogue 1: out float [rows, N]; 2: SwiGLU, out bfloat16 [rows, N / 2].
+extern "C" int fe_gemm_tcgen05_grouped(const void* x, const void* W, void* out, int rows, int experts, int N, int K, int epilogue,
+                                       const int* tiles, const int* tile_expert, const int* tile_row0, const int* offsets,
+                                       int* status, cudaStream_t stream) {
+    FE_REQUIRE(rows >= 1 && experts >= 1 && N >= 1 && K >= 8, "gemm_tcgen05 (grouped): bad sizes rows=%d N=%d K=%d", rows, N, K);
+    FE_REQUIRE(K % 8 == 0, "gemm_tcgen05 (grouped): K = %d must be a multiple of 8 (rows must start on 16-byte boundaries)", K);
+    FE_REQUIRE((((size_t)x | (size_t)W | (size_t)out) & 15) == 0, "gemm_tcgen05 (grouped): operands must be 16-byte aligned");
+    FE_REQUIRE(tiles && tile_expert && tile_row0 && offsets, "gemm_tcgen05 (grouped): the tile list is missing");
+    const long long w_rows_total = (long long)experts * N;
+    if (epilogue == EPI_F32) return launch<EPI_F32>(x, W, out, rows, N, K, status, stream, tiles, tile_expert, tile_row0, offsets, w_rows_total);
+    if (epilogue == EPI_SWIGLU) {
+        FE_REQUIRE(N % 2 == 0, "gemm_tcgen05 (grouped): SwiGLU needs an even number of weight rows, got %d", N);
+        return launch<EPI_SWIGLU>(x, W, out, rows, N, K, status, stream, tiles, tile_expert, tile_row0, offsets, w_rows_total);
+    }
+    FE_REQUIRE(false, "gemm_tcgen05 (grouped): unknown epilogue %d", epilogue);
 }

@@ -676,3 +676,49 @@ extern "C" int fe_routed_experts(const void* h, const int* chosen, const float* 
                    (const bf16*)shared, (bf16*)out, top, D);
     return fe_check_launch("routed_experts");
 }
+
+// ---------------------------------------------------------------------------------------------
+// The pieces on their own, for a caller that takes the two products elsewhere (the grouped tcgen05 GEMM of the
+// bfloat16 library): the plan, the rows of h gathered into sorted order, and the combination.
+extern "C" int fe_routed_plan(const int* chosen, int pairs, int experts, int tile_rows, int* offsets, int* row_of_pair,
+                              int* pair_of_row, int* tiles, int* tile_expert, int* tile_row0, int* status, cudaStream_t stream) {
+    FE_REQUIRE(pairs >= 1 && experts >= 1 && experts <= ROUTE_MAX_EXPERTS && tile_rows >= 1, "routed_plan: bad sizes");
+    fe::launch(route_plan_kernel, 1, 256, 0, stream, chosen, pairs, experts, tile_rows, offsets, row_of_pair, pair_of_row, tiles,
+               tile_expert, tile_row0, status);
+    return fe_check_launch("routed_plan");
+}
+
+namespace {
+// sorted[row] = h[pair_of_row[row] / top]: 16 bytes a thread and step (bytes_per_row is a multiple of 16)
+__global__ void routed_gather_kernel(const uint4* __restrict__ h, const int* __restrict__ pair_of_row, int top,
+                                     uint4* __restrict__ sorted, int pieces) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int row = blockIdx.x;
+    const int src = pair_of_row[row] / top;
+    for (int p = threadIdx.x; p < pieces; p += blockDim.x) sorted[(size_t)row * pieces + p] = h[(size_t)src * pieces + p];
+}
+}  // namespace
+
+extern "C" int fe_routed_gather(const void* h, const int* pair_of_row, int top, void* sorted, int pairs, long long bytes_per_row,
+                                cudaStream_t stream) {
+    FE_REQUIRE(pairs >= 1 && top >= 1 && bytes_per_row > 0 && bytes_per_row % 16 == 0 && ((((size_t)h) | ((size_t)sorted)) & 15) == 0,
+               "routed_gather: rows must be multiples of 16 bytes on 16-byte boundaries");
+    fe::launch(routed_gather_kernel, pairs, 128, 0, stream, (const uint4*)h, pair_of_row, top, (uint4*)sorted, (int)(bytes_per_row / 16));
+    return fe_check_launch("routed_gather");
+}
+
+extern "C" int fe_routed_combine(const float* y, const int* row_of_pair, const float* weights, const void* shared, void* out, int T,
+                                 int top, int D, int dtype, cudaStream_t stream) {
+    FE_REQUIRE(T >= 1 && top >= 1 && D >= 1, "routed_combine: bad sizes");
+    const int threads = D >= 1024 ? 256 : 128;
+    const int stretches = T >= 512 ? 1 : (D + threads - 1) / threads;
+    const dim3 grid(T, stretches < 65535 ? stretches : 65535);
+    if (dtype == FE_F32)
+        fe::launch(routed_combine_kernel<float>, grid, threads, 0, stream, y, row_of_pair, weights, (const float*)shared, (float*)out, top, D);
+    else if (dtype == FE_BF16)
+        fe::launch(routed_combine_kernel<bf16>, grid, threads, 0, stream, y, row_of_pair, weights, (const bf16*)shared, (bf16*)out, top, D);
+    else
+        FE_REQUIRE(false, "routed_combine: unknown dtype %d", dtype);
+    return fe_check_launch("routed_combine");
+}

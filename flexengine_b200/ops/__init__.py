@@ -799,6 +799,49 @@ def route_top(logits, top, scale):
     return chosen, weights
 
 
+ROUTED_TCGEN05_MIN_PAIRS = 1024     # fewer sorted rows than this: the mma.sync tiles of the core library
+ROUTED_TCGEN05_MIN_K = 1024          # narrower experts: level or behind (512 x 384: 0.090 against 0.052 ms at 2,048 rows)
+
+
+def routed_tcgen05_ok(h, pairs, H, F) -> bool:
+    """Whether the two products of a routed feed-forward run on the grouped tcgen05 GEMM: bfloat16, a prompt's worth of
+    rows, widths whose rows start on 16-byte boundaries."""
+    return (h.dtype == torch.bfloat16 and pairs >= ROUTED_TCGEN05_MIN_PAIRS and H % 8 == 0 and F % 8 == 0
+            and min(H, F) >= ROUTED_TCGEN05_MIN_K and h.data_ptr() % 16 == 0)
+
+
+def _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared):
+    """The routed feed-forward with its products on tcgen05 tensor cores: plan (counting sort, row tiles of 128 per
+    expert), the rows of h gathered into sorted order, gate/up with the activation in the epilogue, down into float32,
+    combination.  Everything stays on the device."""
+    T, H = h.shape
+    experts, F2, _ = gate_up.shape
+    F, top = F2 // 2, chosen.shape[1]
+    pairs = T * top
+    most_tiles = -(-pairs // 128) + experts
+    dev = h.device
+    plan = torch.empty(experts + 1 + 2 * pairs + 4 + 2 * most_tiles, dtype=torch.int32, device=dev)
+    offsets, rest = plan[:experts + 1], plan[experts + 1:]
+    row_of_pair, pair_of_row, rest = rest[:pairs], rest[pairs:2 * pairs], rest[2 * pairs:]
+    tiles, tile_expert, tile_row0 = rest[:4], rest[4:4 + most_tiles], rest[4 + most_tiles:4 + 2 * most_tiles]
+    status = status_word(dev)
+    core, tensor = _core(), _bf16()
+    _run(core, "fe_routed_plan", _ptr(chosen), _c_int(pairs), _c_int(experts), _c_int(128), _ptr(offsets), _ptr(row_of_pair),
+         _ptr(pair_of_row), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(status), _stream())
+    rows = torch.empty((pairs, H), dtype=torch.bfloat16, device=dev)
+    _run(core, "fe_routed_gather", _ptr(h), _ptr(pair_of_row), _c_int(top), _ptr(rows), _c_int(pairs), _c_ll(H * 2), _stream())
+    act = torch.empty((pairs, F), dtype=torch.bfloat16, device=dev)
+    _run(tensor, "fe_gemm_tcgen05_grouped", _ptr(rows), _ptr(gate_up), _ptr(act), _c_int(pairs), _c_int(experts), _c_int(2 * F),
+         _c_int(H), _c_int(EPI_SWIGLU), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(offsets), _ptr(status), _stream())
+    y = torch.empty((pairs, H), dtype=torch.float32, device=dev)
+    _run(tensor, "fe_gemm_tcgen05_grouped", _ptr(act), _ptr(down), _ptr(y), _c_int(pairs), _c_int(experts), _c_int(H), _c_int(F),
+         _c_int(EPI_F32), _ptr(tiles), _ptr(tile_expert), _ptr(tile_row0), _ptr(offsets), _ptr(status), _stream())
+    out = torch.empty((T, H), dtype=h.dtype, device=dev)
+    _run(core, "fe_routed_combine", _ptr(y), _ptr(row_of_pair), _ptr(weights), _ptr(shared), _ptr(out), _c_int(T), _c_int(top),
+         _c_int(H), _c_int(_code(h.dtype)), _stream())
+    return out
+
+
 def routed_experts(h, chosen, weights, gate_up, down, shared=None):
     """out[t] = sum_c weights[t, c] * down_e( silu(gate_e h_t) * up_e h_t ) with e = chosen[t, c], plus ``shared`` [T, H] if
     given; gate_up [experts, 2F, H] ([gate; up] per expert), down [experts, H, F].  The (token, choice) pairs are sorted
@@ -812,6 +855,8 @@ def routed_experts(h, chosen, weights, gate_up, down, shared=None):
             or chosen.dtype != torch.int32 or weights.dtype != torch.float32 \
             or (shared is not None and (shared.dtype != h.dtype or shared.shape != h.shape or not shared.is_contiguous())):
         raise ValueError("routed_experts: shapes or dtypes do not fit")
+    if routed_tcgen05_ok(h, T * top, H, F):
+        return _routed_experts_tcgen05(h, chosen, weights, gate_up, down, shared)
     lib = _core()
     need = lib.fe_routed_experts_workspace(_c_int(T), _c_int(top), _c_int(experts), _c_int(H), _c_int(F), _c_int(_code(h.dtype)))
     work = torch.empty(need, dtype=torch.uint8, device=h.device)

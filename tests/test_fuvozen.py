@@ -295,23 +295,25 @@ def test_dense_feed_forward_alone(device, dtype):
 
 @pytest.mark.parametrize("device,dtype", CASES)
 @pytest.mark.parametrize("experts,top,shared,D,F", [(5, 2, 16, 48, 24), (3, 3, 0, 48, 24), (70, 1, 8, 48, 24), (4, 2, 12, 44, 20),
-                                                     (6, 2, 0, 136, 72)])
+                                                     (6, 2, 0, 136, 72), (3, 2, 0, 1024, 1032)])
 def test_routed_feed_forward_alone(device, dtype, experts, top, shared, D, F):
-    """Also widths that are no multiples of 8 (rows off 16-byte boundaries) and tiles with edges on every side."""
+    """Also widths that are no multiples of 8 (rows off 16-byte boundaries), tiles with edges on every side, and a size
+    at which the bfloat16 products take the grouped tcgen05 GEMM (1,280 sorted rows, experts of 1,024 x 1,032)."""
     torch.manual_seed(4)
     dt = getattr(torch, dtype)
-    T = 70 if D < 100 else 300
-    weights = {"router": torch.randn(experts, D)}
+    T = 70 if D < 100 else (300 if D < 1024 else 640)
+    spread = 0.2 * (48 / D) ** 0.5                     # outputs of about the same size whatever the width
+    weights = {"router": torch.randn(experts, D) * (48 / D) ** 0.5}          # logits of a few units whatever the width
     names = {"router.weight": ["router"], "experts.gate_up.weight": [], "experts.down.weight": []}
     for e in range(experts):
         for which, shape in (("gate", (F, D)), ("up", (F, D)), ("down", (D, F))):
-            weights[f"e{e}.{which}"] = bf16_exact(torch.randn(*shape) * 0.2)
+            weights[f"e{e}.{which}"] = bf16_exact(torch.randn(*shape) * spread)
         names["experts.gate_up.weight"] += [f"e{e}.gate", f"e{e}.up"]
         names["experts.down.weight"].append(f"e{e}.down")
     spec = {"router": {"experts": experts, "top": top, "scale": 1.7}}
     if shared:
         for which, shape in (("gate", (shared, D)), ("up", (shared, D)), ("down", (D, shared))):
-            weights[f"shared.{which}"] = bf16_exact(torch.randn(*shape) * 0.2)
+            weights[f"shared.{which}"] = bf16_exact(torch.randn(*shape) * spread)
         names.update({"shared.gate_up.weight": ["shared.gate", "shared.up"], "shared.down.weight": ["shared.down"]})
         spec["shared"] = {"ff": shared}
     part = build_part("feed_forward", PartSpec("routed_experts", {"hidden_size": D, "experts": experts, "top": top, "expert_size": F,
