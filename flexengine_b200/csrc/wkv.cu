@@ -79,9 +79,8 @@ extern "C" int fe_token_shift_blend(const void* h, const float* mu, float* state
 // device (a prompt of one request) or is one (a decode step of many requests).  A seat below 0 (a padding request)
 // starts from zero and keeps nothing.
 constexpr int WKV_TILE = 8;
-constexpr int WKV_GROUPS = 8;
 
-template <typename T, int IPT, int PER>
+template <typename T, int IPT, int PER, bool TWO, int G>
 __global__ void __launch_bounds__(512) wkv_recurrence_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                                       const float* __restrict__ logits, const float* __restrict__ w0,
                                       const float* __restrict__ u, float* state, long long state_stride,
@@ -90,7 +89,8 @@ __global__ void __launch_bounds__(512) wkv_recurrence_kernel(const T* __restrict
     griddep_wait();
     griddep_launch_dependents();
     constexpr int GP = IPT + 4;                   // a group's stretch in shared memory, padded against bank conflicts
-    constexpr int ROW = WKV_GROUPS * GP;
+    constexpr int ROW = G * GP;                   // G groups of key channels a warp (8 or 16)
+    constexpr int LANES_J = 32 / G;               // lanes of a group: value channels side by side
     extern __shared__ __align__(16) float smem[];
     float* rs = smem;                             // [TILE][ROW]
     float* ks = rs + WKV_TILE * ROW;
@@ -98,12 +98,13 @@ __global__ void __launch_bounds__(512) wkv_recurrence_kernel(const T* __restrict
     float* vs = ws + WKV_TILE * ROW;              // [TILE][columns of this block]
     const int req = blockIdx.x, head = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int columns = (blockDim.x >> 5) * 8;    // value channels of this block
+    constexpr int WARP_COLUMNS = LANES_J * (TWO ? 2 : 1);     // TWO: a thread owns two value channels, else one (half the chain a token)
+    const int columns = (blockDim.x >> 5) * WARP_COLUMNS;    // value channels of this block
     const int j0 = blockIdx.z * columns;
-    const int group = lane >> 2;
-    const int local = warp * 8 + (lane & 3) * 2;  // this thread's two value channels within the block's slice
+    const int group = lane / LANES_J;
+    const int local = warp * WARP_COLUMNS + (lane % LANES_J) * (TWO ? 2 : 1);  // this thread's value channels within the block's slice
     const int j = j0 + local;
-    const bool own0 = j < d, own1 = j + 1 < d;
+    const bool own0 = j < d, own1 = TWO && j + 1 < d;
     const int seat = seats[req];
     const bool seated = seat >= 0 && seat < n_seats;
     float* mine = seated ? state + (size_t)seat * state_stride + (size_t)head * d * d : nullptr;
@@ -181,7 +182,9 @@ __global__ void __launch_bounds__(512) wkv_recurrence_kernel(const T* __restrict
         __syncthreads();
         if (t0 + WKV_TILE < end) fetch(t0 + WKV_TILE);
         auto walk = [&](int tt) {
-            const float2 vj = *reinterpret_cast<const float2*>(vs + tt * columns + local);
+            float2 vj;
+            if (TWO) vj = *reinterpret_cast<const float2*>(vs + tt * columns + local);
+            else vj = make_float2(vs[tt * columns + local], 0.f);
             const float* rt = rs + tt * ROW + group * GP;
             const float* kt = ks + tt * ROW + group * GP;
             const float* wt = ws + tt * ROW + group * GP;
@@ -196,15 +199,17 @@ __global__ void __launch_bounds__(512) wkv_recurrence_kernel(const T* __restrict
                 for (int y = 0; y < 4; ++y) {
                     const float kv0 = kk[y] * vj.x, kv1 = kk[y] * vj.y;
                     acc0 = fmaf(rr[y], fmaf(bonus[x + y], kv0, S0[x + y]), acc0);
-                    acc1 = fmaf(rr[y], fmaf(bonus[x + y], kv1, S1[x + y]), acc1);
                     S0[x + y] = fmaf(ww[y], S0[x + y], kv0);
-                    S1[x + y] = fmaf(ww[y], S1[x + y], kv1);
+                    if (TWO) {
+                        acc1 = fmaf(rr[y], fmaf(bonus[x + y], kv1, S1[x + y]), acc1);
+                        S1[x + y] = fmaf(ww[y], S1[x + y], kv1);
+                    }
                 }
             }
 #pragma unroll
-            for (int o = 4; o < 32; o <<= 1) {
+            for (int o = LANES_J; o < 32; o <<= 1) {
                 acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
-                acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
+                if (TWO) acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
             }
             if (group == 0) {
                 float* o = out + (size_t)(t0 + tt) * inner + (size_t)head * d + j;
@@ -230,32 +235,44 @@ __global__ void __launch_bounds__(512) wkv_recurrence_kernel(const T* __restrict
     }
 }
 
-template <typename T, int IPT>
+template <typename T, int IPT, int G>
 static int launch_wkv(const void* r, const void* k, const void* v, const float* logits, const float* w0, const float* u,
                       float* state, long long state_stride, const int* seats, const int* cu_q, float* out, int requests,
                       int heads, int d, int n_seats, cudaStream_t stream) {
-    // a warp per 8 value channels; a head is cut into slices until the blocks about fill the device twice, but a block
-    // keeps four warps at least: every block stages r, k and the decay of all key channels for itself (measured at 32
-    // heads of 64 and one prompt of 2,048 tokens: one warp a block 1.36 ms, two 0.84, four 0.47, eight 0.84)
-    const int head_warps = (d + 7) / 8;
+    // A warp per 8 value channels (two a thread) when the step has blocks to fill the device several times over, else per 4
+    // (one a thread): a block walks its tokens one after the other, so with few blocks what counts is how long one warp
+    // needs for a token, and half the channels are half the chain (one prompt of 2,048 tokens, 32 heads of 64: 0.42 ms with
+    // two a thread).  A head is cut into slices until the blocks about fill the device twice, but a block keeps four warps
+    // at least: every block stages r, k and the decay of all key channels for itself (one value channel a thread: four
+    // slices of four warps 0.34 ms, two of eight 0.53).
     const long long units = (long long)requests * heads;
-    const int most = head_warps / 4 > 1 ? head_warps / 4 : 1;
+    const bool two = G == 8 && units >= 4LL * fe_sm_count();
+    const int warp_columns = (32 / G) * (two ? 2 : 1);
+    const int head_warps = (d + warp_columns - 1) / warp_columns;
+    const int most = head_warps / 4 > 1 ? head_warps / 4 : 1;      // a block keeps four warps at least (two: 0.55 ms)
     int slices = (int)((2LL * fe_sm_count() + units - 1) / units);
     slices = slices < 1 ? 1 : (slices > most ? most : slices);
     int warps = (head_warps + slices - 1) / slices;
+    if (warps > 16) warps = 16;                                    // 512 threads a block
     slices = (head_warps + warps - 1) / warps;
     // a thread stages at most PER elements of r, k and the decay of a tile: TILE x d over 32 x warps threads
     const int need = (WKV_TILE * d + warps * 32 - 1) / (warps * 32);
-    const size_t smem = ((size_t)3 * WKV_TILE * WKV_GROUPS * (IPT + 4) + (size_t)WKV_TILE * warps * 8) * sizeof(float);
-#define FE_WKV_LAUNCH(PER)                                                                                                        \
-    fe::launch(wkv_recurrence_kernel<T, IPT, PER>, dim3(requests, heads, slices), warps * 32, smem, stream, (const T*)r, (const T*)k, \
+    const size_t smem = ((size_t)3 * WKV_TILE * G * (IPT + 4) + (size_t)WKV_TILE * warps * warp_columns) * sizeof(float);
+#define FE_WKV_LAUNCH2(PER, TWO)                                                                                                       \
+    fe::launch(wkv_recurrence_kernel<T, IPT, PER, TWO, G>, dim3(requests, heads, slices), warps * 32, smem, stream, (const T*)r, (const T*)k, \
                (const T*)v, logits, w0, u, state, state_stride, seats, cu_q, out, heads, d, n_seats)
+#define FE_WKV_LAUNCH(PER)             \
+    do {                               \
+        if (G == 8 && two) FE_WKV_LAUNCH2(PER, (G == 8)); \
+        else FE_WKV_LAUNCH2(PER, false);    \
+    } while (0)
     if (need <= 2) FE_WKV_LAUNCH(2);
     else if (need <= 4) FE_WKV_LAUNCH(4);
     else if (need <= 8) FE_WKV_LAUNCH(8);
     else if (need <= 16) FE_WKV_LAUNCH(16);
     else FE_WKV_LAUNCH(32);
 #undef FE_WKV_LAUNCH
+#undef FE_WKV_LAUNCH2
     return fe_check_launch("wkv_recurrence");
 }
 
@@ -263,10 +280,11 @@ template <typename T>
 static int dispatch_wkv(const void* r, const void* k, const void* v, const float* logits, const float* w0, const float* u,
                         float* state, long long state_stride, const int* seats, const int* cu_q, float* out, int requests,
                         int heads, int d, int n_seats, cudaStream_t stream) {
-#define FE_WKV(IPT) return launch_wkv<T, IPT>(r, k, v, logits, w0, u, state, state_stride, seats, cu_q, out, requests, heads, d, n_seats, stream)
-    if (d <= 32) FE_WKV(4);
-    if (d <= 64) FE_WKV(8);
-    FE_WKV(16);
+#define FE_WKV(IPT, G) return launch_wkv<T, IPT, G>(r, k, v, logits, w0, u, state, state_stride, seats, cu_q, out, requests, heads, d, n_seats, stream)
+    // (sixteen groups of key channels a warp, two value channels across, were measured too: 0.61 against 0.34 ms)
+    if (d <= 32) FE_WKV(4, 8);
+    if (d <= 64) FE_WKV(8, 8);
+    FE_WKV(16, 8);
 #undef FE_WKV
 }
 
