@@ -10,7 +10,6 @@ prefill step and in a decode step run kernel by kernel.
 from __future__ import annotations
 
 import json
-import types
 
 from .clocks import ClockSampler, load_peaks
 from .timing import Timer
