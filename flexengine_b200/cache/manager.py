@@ -6,8 +6,8 @@ The reference keeps one pool for all layers and one table per request
 keys, a window of keys, fixed-size state) has its own pool and its own table per
 request, with a page size of its own where its spec names one, so that layers with different
 needs share neither a page size nor a lifetime.
-A request's pages are given back when it ends (allocator.py:103-105) or, in a window
-group, once the window has passed them.  ``reserve`` is atomic across groups.
+A request's pages are given back when it ends (allocator.py:103-105) or, in a window or
+chunk group, once the window or the chunk of the next token has passed them.  ``reserve`` is atomic across groups.
 
 Storage of a paged group: ``[slots, planes, pages, kv_heads, page_size, head_dim]`` (keys at
 index 0, values at 1; a group of one plane keeps a single vector per token that serves as both), so one
@@ -99,7 +99,7 @@ class CacheManager:
         self.requests: dict[str, RequestCache] = {}
         self.free_state_slots = list(range(self.max_requests - 1, -1, -1))
         self._paged = [(gi, g) for gi, g in enumerate(self.groups) if isinstance(g, PagedGroup)]
-        self._windowed = [(gi, g) for gi, g in self._paged if g.spec.kind == "window" and g.spec.window > 0]
+        self._windowed = [(gi, g) for gi, g in self._paged if g.spec.kind in ("window", "chunk") and g.spec.window > 0]
         self.chunk_granularity = math.lcm(*[int(getattr(spec, "chunk_granularity", 1)) for spec in self.specs] or [1])
         # complete pages in every group: what may be shared between requests
         self.sharing_unit = math.lcm(*[g.page_size for _, g in self._paged] or [1])
@@ -197,8 +197,12 @@ class CacheManager:
         rc.tokens = target
         for gi, g in self._windowed:
             w = g.spec.window
-            # the next query sits at position >= rc.tokens and sees keys t > position - w
-            first_needed = rc.tokens - w + 1
+            if g.spec.kind == "chunk":
+                # the next query sits at position >= rc.tokens and sees no key before the start of its chunk
+                first_needed = rc.tokens // w * w
+            else:
+                # the next query sits at position >= rc.tokens and sees keys t > position - w
+                first_needed = rc.tokens - w + 1
             table = rc.tables[gi]
             for j in range(min(len(table), max(0, first_needed) // g.page_size)):
                 if table[j] != RELEASED:

@@ -1,1 +1,1 @@
-from . import fuvozen, qwen2  # noqa: F401  (register Fuvozen and Qwen2ForCausalLM)
+from . import fuvozen, fuvuvik, qwen2  # noqa: F401  (register Fuvozen, Fuvuvik and Qwen2ForCausalLM)

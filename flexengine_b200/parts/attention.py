@@ -11,6 +11,8 @@ from __future__ import annotations
 
 import math
 
+import torch
+
 from .base import Mixer, build_part, register_mixer
 from .spec import PartSpec
 
@@ -83,4 +85,91 @@ class AttentionMixer(Mixer):
         return ops.linear(out, self.out_weight, self.out_bias)
 
 
+class GatedAttentionMixer(Mixer):
+    """Grouped-query attention with the options some designs add, each a parameter:
+
+    ``conv`` > 0: a causal convolution of that many taps over time on every channel of the projected q, k and v
+    (y_t = sum_j w[:, j] u_(t - conv + 1 + j), zeros before the sequence's start), before everything else; the last
+    conv - 1 projected rows of a request are kept in a state slot (``conv_group``, ``conv_slot``).
+    ``rot_dims``: the first that many entries of every query and key head turn by position * rot_base^(-2i/rot_dims),
+    entry i paired with i + rot_dims/2; the rest pass unchanged.
+    ``qk_norm``: queries and keys are then divided by their root mean square over the head (eps inside the root).
+    ``mask``: "full" (every earlier key), "window" (the last ``mask_size`` keys) or "chunk" (the earlier keys of the
+    query's own chunk of ``mask_size`` positions, counted from position 0 of the sequence).
+    ``sink``: 1 is added to the softmax's denominator, as if every query also saw a key of score 0 and value 0.
+    Every head's output is multiplied by sigmoid(w_g,h . x), x the rows the projections read.  The value size may differ
+    from the query/key size: the cache and the attention kernels run at ``head`` = the larger, in steps of 16, the
+    smaller padded with zeros (scores and outputs are the same).  No biases.
+
+    q, k, v and the head gates are one product; convolution, rotation, unit norm and the cache write are one kernel;
+    angles, norms, scores and softmax are float32."""
+
+    MASKS = ("full", "window", "chunk")
+
+    def __init__(self, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, rot_base: float = 10000.0,
+                 rot_dims: int = 0, conv: int = 0, qk_norm: bool = False, eps: float = 1e-6, mask: str = "full", mask_size: int = 0,
+                 sink: bool = False, conv_group: int = -1, conv_slot: int = -1):
+        if heads % kv_heads:
+            raise ValueError("Invalid GQA head ratio")
+        if mask not in self.MASKS or (mask != "full" and mask_size <= 0):
+            raise ValueError(f"mask {mask!r} of size {mask_size}: known masks are {', '.join(self.MASKS)}; all but 'full' need a size")
+        if rot_dims % 2 or rot_dims > dim:
+            raise ValueError("rot_dims must be even and at most dim")
+        self.hidden_size, self.heads, self.kv_heads, self.dim, self.vdim = int(hidden_size), int(heads), int(kv_heads), int(dim), int(vdim)
+        self.scale, self.rot_base, self.rot_dims, self.conv = float(scale), float(rot_base), int(rot_dims), int(conv)
+        self.qk_norm, self.eps, self.mask, self.mask_size, self.sink = bool(qk_norm), float(eps), mask, int(mask_size), bool(sink)
+        self.conv_group, self.conv_slot = int(conv_group), int(conv_slot)
+        if self.conv > 1 and self.conv_group < 0:
+            raise ValueError("a convolution of more than one tap needs a state slot for its history")
+        self.head = -(-max(self.dim, self.vdim) // 16) * 16
+        if self.head > 1024:
+            raise ValueError(f"head size {self.head}: the attention kernels take up to 1024")
+        self.qkvg_weight = self.conv_weight = self.o_weight = None
+        self._inv_freq = {}
+
+    @property
+    def channels(self) -> int:
+        return (self.heads + self.kv_heads) * self.dim + self.kv_heads * self.vdim
+
+    def parameter_shapes(self) -> dict:
+        shapes = {"qkvg.weight": ((self.channels + self.heads, self.hidden_size), "matrix"),
+                  "o.weight": ((self.hidden_size, self.heads * self.vdim), "matrix")}
+        if self.conv > 0:
+            shapes["conv.weight"] = ((self.channels, self.conv), "vector")
+        return shapes
+
+    def reads_first(self):
+        return self.qkvg_weight
+
+    def cache_need(self):
+        return {"kind": self.mask, "kv_heads": self.kv_heads, "head_dim": self.head, "window": self.mask_size}
+
+    def inverse_frequencies(self, device):
+        key = str(device)
+        if key not in self._inv_freq:
+            i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
+            table = torch.pow(torch.tensor(self.rot_base, dtype=torch.float64), -2.0 * i / max(self.rot_dims, 1))
+            self._inv_freq[key] = table.to(torch.float32).to(device).contiguous()
+        return self._inv_freq[key]
+
+    def forward(self, ctx, h, entry):
+        ops = ctx.ops
+        group = ctx.groups[entry.cache_group]
+        k_cache, v_cache = group.kv_slot(entry.cache_slot)
+        slot_mapping = group.slot_mapping if entry.write_cache else None
+        history = ctx.groups[self.conv_group].state(self.conv_slot) if self.conv > 1 else None
+        projected = ops.linear(h, self.qkvg_weight)                          # [T, channels + heads]
+        queries = ops.qkv_conv_rope_norm_cache(
+            projected, self.conv_weight, history, self.conv, ctx.state_slots, ctx.cu_q, ctx.token_request, ctx.positions,
+            self.inverse_frequencies(h.device) if self.rot_dims else None, self.rot_dims, self.qk_norm, self.eps, slot_mapping,
+            k_cache, v_cache, self.heads, self.kv_heads, self.dim, self.vdim, self.head, group.page_size)
+        # one int says what a query sees: 0 every earlier key, w > 0 the last w, -c < 0 its own chunk of c positions
+        visibility = {"full": 0, "window": self.mask_size, "chunk": -self.mask_size}[self.mask]
+        mixed = ops.paged_attention(queries, k_cache, v_cache, group.block_table, ctx, self.heads, self.kv_heads, self.head,
+                                    group.page_size, self.scale, visibility, sink=self.sink)
+        gated = ops.head_gate(mixed, projected, self.channels, self.heads, self.head, self.vdim)
+        return ops.linear(gated, self.o_weight)
+
+
 register_mixer("attention", AttentionMixer)
+register_mixer("gated_attention", GatedAttentionMixer)

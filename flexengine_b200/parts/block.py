@@ -169,5 +169,47 @@ class ParallelDepthAverageBlock:
         return None
 
 
+class HyperGatedBlock:
+    """A layer over S residual streams x [S, T, width] (float32).  Sublayer q (1: the mixer, 2: the feed-forward, if
+    the layer has one):
+        h = norm_q(sum_s read_q[s] x_s);  y = sublayer(h) * sigmoid(W_rg h + b_rg);
+        x_t <- sum_s mix_q[s, t] x_s + write_q[t] * y      (every stream from the old ones)
+    and the mixer reads h blended with the row of the token before (``TokenShift``), the gate the rows as they are.
+    A sublayer's y is not put into the streams at once: it is handed on as ``pending`` and the kernel of the norm that
+    reads the streams next does it (the next sublayer's, the next layer's, or the model's final norm)."""
+
+    def __init__(self, layer_spec):
+        from .streams import HyperConnection, ResidualGate, TokenShift
+        params = dict(layer_spec.block_params)
+        streams, width = int(params["streams"]), int(params["hidden_size"])
+        self.norm1 = build_part("norm", layer_spec.norm)
+        self.mixer = build_part("mixer", layer_spec.mixer)
+        self.hc1, self.rg1 = HyperConnection(streams), ResidualGate(width)
+        self.shift = TokenShift(width, params["shift_group"], params["shift_slot"])
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward) if layer_spec.feed_forward is not None else None
+        self.part_names = ("norm1", "hc1", "rg1", "shift", "mixer")
+        if self.feed_forward is not None:
+            self.norm2 = build_part("norm", layer_spec.norm)
+            self.hc2, self.rg2 = HyperConnection(streams), ResidualGate(width)
+            self.part_names += ("norm2", "hc2", "rg2", "feed_forward")
+
+    def parts(self) -> dict:
+        return {name: getattr(self, name) for name in self.part_names}
+
+    def forward(self, ctx, residual, pending, entry):
+        from .streams import StreamUpdate
+        h = self.norm1.forward(ctx, residual, pending, read=self.hc1.read)
+        gate = self.rg1.logits(ctx, h)
+        y = self.mixer.forward(ctx, self.shift.forward(ctx, h), entry)
+        pending = StreamUpdate(y, gate, self.rg1.bias, self.hc1.mix, self.hc1.write)
+        if self.feed_forward is None:
+            return pending
+        h = self.norm2.forward(ctx, residual, pending, read=self.hc2.read)
+        gate = self.rg2.logits(ctx, h)
+        y = self.feed_forward.forward(ctx, h)
+        return StreamUpdate(y, gate, self.rg2.bias, self.hc2.mix, self.hc2.write)
+
+
 register_block("prenorm", PreNormBlock)
+register_block("hyper_gated", HyperGatedBlock)
 register_block("parallel_depth_average", ParallelDepthAverageBlock)

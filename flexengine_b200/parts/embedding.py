@@ -2,6 +2,8 @@
 
 x = embed_tokens.weight[ids] over the step's flattened tokens
 (src/flexengine/inference/models/qwen2.py:90,94).  The stream is float32 whatever the table's dtype.
+A design may scale the rows by a constant, and may start several copies of the stream at once
+(``streams``: the result is then [streams, T, hidden], every copy the same).
 """
 from __future__ import annotations
 
@@ -9,15 +11,18 @@ from .base import Embedding, register_embedding
 
 
 class TokenEmbedding(Embedding):
-    def __init__(self, vocab_size: int, hidden_size: int):
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, streams: int | None = None):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.scale, self.streams = float(scale), None if streams is None else int(streams)
         self.weight = None
 
     def parameter_shapes(self) -> dict:
         return {"weight": ((self.vocab_size, self.hidden_size), "matrix")}
 
     def forward(self, ctx):
-        return ctx.ops.embedding(ctx.token_ids, self.weight)
+        if self.scale == 1.0 and self.streams is None:
+            return ctx.ops.embedding(ctx.token_ids, self.weight)
+        return ctx.ops.embedding(ctx.token_ids, self.weight, scale=self.scale, streams=self.streams)
 
 
 class HashedPairEmbedding(Embedding):

@@ -1,4 +1,4 @@
-"""Dense SwiGLU feed-forward: down( silu(gate(h)) * up(h) ).
+"""Dense gated feed-forward: down( act(gate(h)) * up(h) ), act = silu (SwiGLU) or the tanh form of GELU.
 
 Formula: tests/unit/test_synthetic_qwen.py:30-36 of the reference (its product code
 calls the module opaquely, src/flexengine/inference/models/qwen2.py:130).  gate and up
@@ -12,9 +12,14 @@ from .base import FeedForward, register_feed_forward
 class SwiGLU(FeedForward):
     takes_prenormed = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    ACTIVATIONS = ("silu", "gelu_tanh")
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"unknown gate activation {activation!r}; known: {', '.join(self.ACTIVATIONS)}")
+        self.activation = activation
         self.gate_up_weight = None
         self.down_weight = None
 
@@ -26,6 +31,9 @@ class SwiGLU(FeedForward):
         return self.gate_up_weight
 
     def forward(self, ctx, h, follow=None, upcoming=None):
+        if self.activation != "silu":
+            act = ctx.ops.linear_gated(h, self.gate_up_weight, self.intermediate_size, self.activation)
+            return ctx.ops.linear(act, self.down_weight)
         if follow is None and upcoming is None:
             return ctx.ops.linear(ctx.ops.linear_swiglu(h, self.gate_up_weight, self.intermediate_size), self.down_weight)
         # a decode step on kernels that take the hints: each product is told which matrix is streamed after it
@@ -93,5 +101,6 @@ class RoutedExperts(FeedForward):
 
 
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("gated_mlp", SwiGLU)
 register_feed_forward("xielu_mlp", XieluMlp)
 register_feed_forward("routed_experts", RoutedExperts)

@@ -51,5 +51,24 @@ class GroupRMSNorm(Norm):
         return ctx.ops.add_group_rmsnorm(residual, delta, self.weight, self.eps, self.groups, ctx.dtype, rows)
 
 
+class StreamRMSNorm(Norm):
+    """RMSNorm of a learned sum of several residual streams: u = sum_s read[s] x_s over the streams x [S, T, hidden]
+    (``read`` None: the plain sum), y = w * u * rsqrt(mean(u^2) + eps), all float32.  What the sublayer before left
+    (``delta``: an object with ``y``, ``gate``, ``gate_bias``, ``mix`` and ``write``) is put into the streams first, in
+    the same kernel: x_t <- sum_s mix[s, t] x_s + write[t] * y * sigmoid(gate + gate_bias), every stream from the old
+    ones.  With ``rows`` only those rows are read and nothing is written back."""
+
+    def __init__(self, hidden_size: int, eps: float, streams: int):
+        self.hidden_size, self.eps, self.streams = int(hidden_size), float(eps), int(streams)
+        self.weight = None
+
+    def parameter_shapes(self) -> dict:
+        return {"weight": ((self.hidden_size,), "vector")}
+
+    def forward(self, ctx, residual, delta, rows=None, read=None):
+        return ctx.ops.stream_rmsnorm(residual, read, self.weight, self.eps, ctx.dtype, update=delta, rows=rows)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("stream_rmsnorm", StreamRMSNorm)
 register_norm("group_rmsnorm", GroupRMSNorm)

@@ -27,6 +27,9 @@ class CacheGroupSpec:
     kind "full":   paged keys/values, every key kept.
     kind "window": paged keys/values, only the last ``window`` keys are visible; pages
                    that the window has passed are given back.
+    kind "chunk":  paged keys/values, a query sees only the earlier keys of its own chunk of ``window``
+                   positions (counted from position 0 of the sequence); pages that lie wholly before the
+                   chunk of the next token are given back.
     kind "state":  a fixed-size per-request slot (``state_shape`` elements of ``state_dtype``),
                    zeroed at admission.
     ``slots`` is the number of cache slots in the group (one per run entry that writes).
@@ -54,10 +57,10 @@ class CacheGroupSpec:
             raise ValueError("a paged group keeps one or two tensors per token")
         if self.page_size < 0 or self.chunk_granularity < 1:
             raise ValueError("page_size must be >= 0 and chunk_granularity >= 1")
-        if self.kind not in ("full", "window", "state"):
+        if self.kind not in ("full", "window", "chunk", "state"):
             raise ValueError(f"unknown cache group kind {self.kind!r}")
-        if self.kind == "window" and self.window <= 0:
-            raise ValueError("a window group needs window > 0")
+        if self.kind in ("window", "chunk") and self.window <= 0:
+            raise ValueError("a window or chunk group needs window > 0")
 
 
 @dataclass(frozen=True)

@@ -12,8 +12,9 @@ import math
 import torch
 
 
-def embedding(token_ids, table):
-    return table[token_ids.long()].float()
+def embedding(token_ids, table, scale=1.0, streams=None):
+    rows = table[token_ids.long()].float() * scale
+    return rows if streams is None else rows[None].repeat(streams, 1, 1)
 
 
 def carry_tokens(token_ids, rows, sources, previous):
@@ -51,6 +52,22 @@ def linear_swiglu(x, w, intermediate):
     return swiglu(linear(x, w), intermediate)
 
 
+def gated_activation(gate_up, intermediate, activation):
+    g = gate_up[:, :intermediate].float()
+    u = gate_up[:, intermediate:].float()
+    if activation == "silu":
+        a = g / (1.0 + torch.exp(-g))
+    elif activation == "gelu_tanh":
+        a = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g * g * g)))
+    else:
+        raise ValueError(activation)
+    return (a * u).to(gate_up.dtype)
+
+
+def linear_gated(x, w, intermediate, activation):
+    return gated_activation(linear(x, w), intermediate, activation)
+
+
 def qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache,
                         nq, nkv, d, page_size, src=None):
     """``src``: the projection in float32 when it was kept so; else ``qkv`` is rewritten in place."""
@@ -85,8 +102,11 @@ def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, 
     return qkv
 
 
-def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window, upcoming=None):
+def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window, upcoming=None, sink=False):
+    """``window`` > 0: the last ``window`` keys; < 0: the earlier keys of the query's chunk of -window positions.
+    ``sink``: 1 is added to the softmax's denominator."""
     T = qkv.shape[0]
+    chunk, window = (-window, 0) if window < 0 else (0, window)
     out = torch.zeros(T, nq * d, dtype=qkv.dtype, device=qkv.device)
     q_all = qkv[:, :nq * d].float().view(T, nq, d)
     cu = ctx.cu_q.tolist()
@@ -96,7 +116,7 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
         q = q_all[cu[r]:cu[r + 1]]
         n = q.shape[0]
         length = starts[r] + n
-        lo = max(0, starts[r] - window + 1) if window > 0 else 0
+        lo = max(0, starts[r] - window + 1) if window > 0 else (starts[r] // chunk * chunk if chunk else 0)
         lo_page = lo // page_size
         pages = block_table[r, lo_page:-(-length // page_size)].long()
         k = k_cache[pages].float().permute(0, 2, 1, 3).reshape(-1, nkv, d)      # [tokens, nkv, d]
@@ -106,15 +126,137 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
         visible = (key_pos[None, :] <= q_pos[:, None]) & (key_pos[None, :] < length)
         if window > 0:
             visible &= key_pos[None, :] > q_pos[:, None] - window
+        if chunk:
+            visible &= key_pos[None, :] // chunk == q_pos[:, None] // chunk
         kh = k.repeat_interleave(ratio, dim=1)
         vh = v.repeat_interleave(ratio, dim=1)
         scores = torch.einsum("qhd,thd->hqt", q, kh) * scale
         scores = scores.masked_fill(~visible[None], float("-inf"))
-        w = torch.softmax(scores, dim=-1)
+        if sink:
+            top = torch.clamp(scores.max(dim=-1, keepdim=True).values, min=0.0)
+            e = torch.exp(scores - top)
+            w = e / (e.sum(dim=-1, keepdim=True) + torch.exp(-top))
+        else:
+            w = torch.softmax(scores, dim=-1)
         w = torch.where(visible[None], w, torch.zeros_like(w))
         o = torch.einsum("hqt,thd->qhd", w, vh)
         out[cu[r]:cu[r + 1]] = o.reshape(n, nq * d).to(qkv.dtype)
     return out
+
+
+# ---- several residual streams, token shift, gated attention, minGRU ---------------------------------------
+def stream_rmsnorm(streams, read, weight, eps, out_dtype, update=None, rows=None):
+    """u = sum_s read[s] x_s (read None: the plain sum) through an RMSNorm; ``update`` (y, gate, gate_bias, mix, write) is
+    put into the streams first: x_t <- sum_s mix[s, t] x_s + write[t] * y * sigmoid(gate + gate_bias).  With ``rows``
+    only those rows are read and nothing is written back."""
+    x = streams if rows is None else streams[:, rows.long()]
+    if update is not None:
+        y, gate = update.y.float(), update.gate.float()
+        if rows is not None:
+            y, gate = y[rows.long()], gate[rows.long()]
+        gated = y * torch.sigmoid(gate + update.gate_bias.float())
+        x = torch.einsum("st,snd->tnd", update.mix.float(), x) + update.write.float()[:, None, None] * gated[None]
+        if rows is None:
+            streams.copy_(x)
+    u = x.sum(dim=0) if read is None else torch.einsum("s,snd->nd", read.float(), x)
+    return (u * torch.rsqrt(u.pow(2).mean(dim=-1, keepdim=True) + eps) * weight.float()).to(out_dtype)
+
+
+def token_shift(h, mu, kept, state_slots, cu_q, token_request):
+    """h + (h' - h) * mu with h' the row before (the seat's kept row for a portion's first token, zeros for a seat below
+    0); every seat then keeps its request's last row."""
+    hf = h.float()
+    before = torch.zeros_like(hf)
+    cu, seats = cu_q.tolist(), state_slots.tolist()
+    for r in range(len(seats)):
+        a, b = cu[r], cu[r + 1]
+        before[a + 1:b] = hf[a:b - 1]
+        if seats[r] >= 0:
+            before[a] = kept[seats[r]]
+            kept[seats[r]] = hf[b - 1]
+    return (hf + (before - hf) * mu.float()).to(h.dtype)
+
+
+def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, token_request, positions, inv_freq, rot_dims,
+                             qk_norm, eps, slot_mapping, k_cache, v_cache, heads, kv_heads, dim, vdim, head, page_size):
+    """projected [T, >= channels] holds q | k | v.  A causal convolution of ``taps`` taps over time per channel (``conv``
+    [channels, taps]; ``history`` [seats, (taps - 1) channels] holds every request's last taps - 1 projected rows and is
+    brought up to date), rotation of the first ``rot_dims`` entries of the query and key heads, their unit norm, keys and
+    values into the cache and the queries out, both padded with zeros to ``head`` entries a head."""
+    T = projected.shape[0]
+    C = (heads + kv_heads) * dim + kv_heads * vdim
+    u = projected[:, :C].float()
+    if conv is not None:
+        y = torch.zeros_like(u)
+        cu, seats = cu_q.tolist(), state_slots.tolist()
+        back = taps - 1
+        for r in range(len(seats)):
+            a, b = cu[r], cu[r + 1]
+            old = history[seats[r]].view(back, C) if (seats[r] >= 0 and back) else torch.zeros(back, C, device=u.device)
+            rows = torch.cat([old, u[a:b]])
+            for j in range(taps):
+                y[a:b] += conv[:, j].float() * rows[j:j + (b - a)]
+            if seats[r] >= 0 and back:
+                history[seats[r]] = rows[rows.shape[0] - back:].reshape(-1)
+        u = y
+    q = u[:, :heads * dim].reshape(T, heads, dim)
+    k = u[:, heads * dim:(heads + kv_heads) * dim].reshape(T, kv_heads, dim)
+    v = u[:, (heads + kv_heads) * dim:].reshape(T, kv_heads, vdim)
+    if inv_freq is not None and rot_dims > 0:
+        ang = positions.float()[:, None] * inv_freq.float()[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        half = rot_dims // 2
+
+        def turn(x):
+            a, b = x[..., :half], x[..., half:rot_dims]
+            return torch.cat([a * cos - b * sin, b * cos + a * sin, x[..., rot_dims:]], dim=-1)
+        q, k = turn(q), turn(k)
+    if qk_norm:
+        q = q * torch.rsqrt(q.pow(2).mean(dim=-1, keepdim=True) + eps)
+        k = k * torch.rsqrt(k.pow(2).mean(dim=-1, keepdim=True) + eps)
+    dt = projected.dtype
+    queries = torch.zeros(T, heads, head, dtype=dt, device=u.device)
+    queries[..., :dim] = q.to(dt)
+    if slot_mapping is not None:
+        slots = slot_mapping.long()
+        keep = slots >= 0
+        page, off = slots[keep] // page_size, slots[keep] % page_size
+        kp = torch.zeros(T, kv_heads, head, dtype=dt, device=u.device)
+        vp = torch.zeros(T, kv_heads, head, dtype=dt, device=u.device)
+        kp[..., :dim] = k.to(dt)
+        vp[..., :vdim] = v.to(dt)
+        k_cache[page, :, off] = kp[keep]
+        v_cache[page, :, off] = vp[keep]
+    return queries.view(T, heads * head)
+
+
+def head_gate(mixed, projected, offset, heads, head, vdim):
+    """out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(projected[t, offset + h])."""
+    T = mixed.shape[0]
+    gate = torch.sigmoid(projected[:, offset:offset + heads].float())
+    out = mixed.view(T, heads, head)[..., :vdim].float() * gate[:, :, None]
+    return out.reshape(T, heads * vdim).to(mixed.dtype)
+
+
+def mingru_scan(zxg, bias, state, state_slots, cu_q, width, out_dtype, max_q_len=0):
+    """zxg [T, 3 width] float32 (z | x | g before their biases and activations).  z = sigmoid(. + b_z), u = . + b_x,
+    c = u + 1/2 where u >= 0 else sigmoid(u), S <- (1 - z) S + z c from the seat's kept S (zeros for a seat below 0),
+    out = S * silu(g)."""
+    W = width
+    z = torch.sigmoid(zxg[:, :W].float() + bias[:W].float())
+    u = zxg[:, W:2 * W].float() + bias[W:].float()
+    c = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+    g = zxg[:, 2 * W:].float()
+    out = torch.zeros(zxg.shape[0], W, dtype=torch.float32, device=zxg.device)
+    cu, seats = cu_q.tolist(), state_slots.tolist()
+    for r in range(len(seats)):
+        S = state[seats[r]].clone() if seats[r] >= 0 else torch.zeros(W, device=zxg.device)
+        for t in range(cu[r], cu[r + 1]):
+            S = (1.0 - z[t]) * S + z[t] * c[t]
+            out[t] = S
+        if seats[r] >= 0:
+            state[seats[r]] = S
+    return (out * (g / (1.0 + torch.exp(-g)))).to(out_dtype)
 
 
 # ---- hashed pair embedding, grouped norm, depth average ----------------------------------------------
