@@ -3,7 +3,10 @@
 //
 // Math as the reference's block-wise path (inference/attention/paged.py:50-70): running maximum,
 // running sum and value accumulator in float; key t is visible to the query at position p iff
-// t <= p (and t > p - window when window > 0); query head h reads key/value head h / (nq / nkv).
+// t <= p (and t > p - window when window > 0; t in the chunk of -window positions that holds p when window < 0); query
+// head h reads key/value head h / (nq / nkv).  ``sink``: the softmax starts as if a key of score 0 and value 0 had been
+// seen (running maximum 0, running sum 1), which adds 1 to its denominator; of the blocks and warps that share a row's
+// keys, the first one does.
 //
 // Both kernels walk the keys in tiles of 32 aligned to position 0.  A tile's keys and values are
 // gathered page by page with 16-byte asynchronous copies (cp.async) into a ring of shared-memory
@@ -258,7 +261,7 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
                     float* __restrict__ part_o, float* __restrict__ part_lse, const bf16* __restrict__ kc,
                     const bf16* __restrict__ vc, const int* __restrict__ block_table, int bt_stride,
                     const int* __restrict__ cu_q, const int* __restrict__ q_start, int nq, int nkv, int d, int ps,
-                    int num_pages, float scale_log2, int window, int* __restrict__ status) {
+                    int num_pages, float scale_log2, int window, int sink, int* __restrict__ status) {
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -272,7 +275,7 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     const int G = nq / nkv;
     const int tok = cu_q[b];
     const int pos = q_start[b];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = first_visible(pos, window);
     const int tile_lo = lo / TK, tile_hi = pos / TK;
     const int per = (tile_hi - tile_lo + 1 + splits - 1) / splits;
     const int t_begin = tile_lo + split * per, t_end = min(tile_hi + 1, t_begin + per);
@@ -305,6 +308,10 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
 #pragma unroll
     for (int n = 0; n < DMAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+    if (sink && split == 0 && warp == 0) {
+        m[0] = m[1] = 0.f;
+        if (t == 0) l[0] = l[1] = 1.f;              // the four threads of a row add their sums up later
+    }
 
     for (int it = 0; it < n_tiles; ++it) {
         // the stage of tile it - 1 is free (both warps finished it): tile it + AHEAD goes there
@@ -518,7 +525,7 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32)
 paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                      const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
                      int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start, int nq, int nkv,
-                     int d, int ps, int num_pages, float scale_log2, int window, int* __restrict__ status) {
+                     int d, int ps, int num_pages, float scale_log2, int window, int sink, int* __restrict__ status) {
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -538,13 +545,13 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
     const bool v0 = m0 < rows, v1 = m1 < rows;
     const int qi0 = v0 ? m0 / G : 0, qi1 = v1 ? m1 / G : 0;
     const int pos0 = v0 ? start + qi0 : -1, pos1 = v1 ? start + qi1 : -1;
-    const int lo0 = window > 0 ? max(0, pos0 - window + 1) : 0, lo1 = window > 0 ? max(0, pos1 - window + 1) : 0;
+    const int lo0 = first_visible(pos0, window), lo1 = first_visible(pos1, window);
     const int head0 = kvh * G + (v0 ? m0 % G : 0), head1 = kvh * G + (v1 ? m1 % G : 0);
 
     // keys this block needs: from the window edge of its first query to its last query
     const int qi_first = m_block / G, qi_last = min(n_q - 1, (m_block + PREFILL_ROWS - 1) / G);
     const int hi = start + qi_last;
-    const int lo = window > 0 ? max(0, start + qi_first - window + 1) : 0;
+    const int lo = first_visible(start + qi_first, window);
     const int s_begin = lo / PREFILL_KEYS, n_stages = hi / PREFILL_KEYS - s_begin + 1;
     KvSource src{kc, vc, block_table + (size_t)r * bt_stride, nkv, kvh, d, ps, (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1,
                  num_pages};
@@ -564,13 +571,16 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
 #pragma unroll
     for (int n = 0; n < DMAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+    if (sink) {
+        m[0] = m[1] = 0.f;
+        if (t == 0) l[0] = l[1] = 1.f;              // the four threads of a row add their sums up later
+    }
 
     // this warp's rows: the first and last position any of them has, and the widest window edge
     const int w_first = m_block + warp * 16, w_last = min(rows - 1, w_first + 15);
     const bool w_any = w_first < rows;
     const int w_pos_min = w_any ? start + w_first / G : -1, w_pos_max = w_any ? start + w_last / G : -1;
-    const int w_lo_min = window > 0 ? max(0, w_pos_min - window + 1) : 0;
-    const int w_lo_max = window > 0 ? max(0, w_pos_max - window + 1) : 0;
+    const int w_lo_min = first_visible(w_pos_min, window), w_lo_max = first_visible(w_pos_max, window);
 
     for (int it = 0; it < n_stages; ++it) {
         cp_async_wait<0>();
@@ -637,7 +647,7 @@ int check_common(const char* what, int nq, int nkv, int d, int ps, int num_pages
                  long long out_stride) {
     FE_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "%s: bad head counts %d/%d", what, nq, nkv);
     FE_REQUIRE(d >= 16 && d <= 256 && d % 16 == 0, "%s: head size %d is not a multiple of 16 in [16, 256]", what, d);
-    FE_REQUIRE(ps > 0 && num_pages > 0 && window >= 0, "%s: bad page size, page count or window", what);
+    FE_REQUIRE(ps > 0 && num_pages > 0, "%s: bad page size or page count", what);
     FE_REQUIRE(q_stride % 8 == 0 && out_stride % 2 == 0, "%s: row strides must keep 16-byte alignment", what);
     return 0;
 }
@@ -659,7 +669,7 @@ extern "C" long long fe_paged_decode_scratch_bytes(int requests, int nq, int d, 
 extern "C" int fe_paged_decode_mma_upcoming(const void* q, long long q_stride, void* out, long long out_stride, void* scratch,
                                             const void* kc, const void* vc, const int* block_table, int bt_stride,
                                             const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d, int ps,
-                                            int num_pages, float scale, int window, int splits, const void* upcoming,
+                                            int num_pages, float scale, int window, int sink, int splits, const void* upcoming,
                                             long long upcoming_bytes, int* status, cudaStream_t stream) {
     if (check_common("paged_decode", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
     FE_REQUIRE(nq / nkv <= 16, "paged_decode: %d query heads per key/value head; this kernel takes up to 16", nq / nkv);
@@ -676,7 +686,7 @@ extern "C" int fe_paged_decode_mma_upcoming(const void* q, long long q_stride, v
         if (allow_smem(paged_decode_kernel<DMAX, UPPER>, decode_smem<DMAX>(), "paged_decode")) return 1;          \
         fe::launch(paged_decode_kernel<DMAX, UPPER>, grid, DECODE_WARPS * 32, decode_smem<DMAX>(), stream,                               \
             (const bf16*)q, q_stride, (bf16*)out, out_stride, part_o, part_lse, (const bf16*)kc, (const bf16*)vc, \
-            block_table, bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, status);        \
+            block_table, bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, sink, status);  \
     } while (0)
     const bool upper = nq / nkv > 8;
     if (d <= 64) { if (upper) FE_DECODE(64, true); else FE_DECODE(64, false); }
@@ -750,7 +760,7 @@ extern "C" int fe_paged_decode_cluster_resident(int requests, int nq, int nkv, i
 extern "C" int fe_paged_decode_cluster(const void* q, long long q_stride, void* out, long long out_stride,
                                        const void* kc, const void* vc, const int* block_table, int bt_stride,
                                        const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d, int ps,
-                                       int num_pages, float scale, int window, int splits, int* status,
+                                       int num_pages, float scale, int window, int sink, int splits, int* status,
                                        cudaStream_t stream) {
     if (check_common("paged_decode", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
     FE_REQUIRE(nq / nkv <= 16, "paged_decode: %d query heads per key/value head; this kernel takes up to 16", nq / nkv);
@@ -790,7 +800,7 @@ extern "C" int fe_paged_decode_cluster(const void* q, long long q_stride, void* 
         cfg.dynamicSmemBytes = decode_smem<DMAX>(STAGES);                                                              \
         const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, (const bf16*)q, q_stride, (bf16*)out, out_stride,     \
             (float*)nullptr, (float*)nullptr, (const bf16*)kc, (const bf16*)vc, block_table, bt_stride, cu_q, q_start, \
-            nq, nkv, d, ps, num_pages, scale_log2, window, status);                                                    \
+            nq, nkv, d, ps, num_pages, scale_log2, window, sink, status);                                              \
         FE_REQUIRE(err == cudaSuccess, "paged_decode (cluster of %d): %s", splits, cudaGetErrorString(err));           \
     } while (0)
     const bool upper = nq / nkv > 8;
@@ -808,13 +818,13 @@ extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out,
                                    int num_pages, float scale, int window, int splits, int* status,
                                    cudaStream_t stream) {
     return fe_paged_decode_mma_upcoming(q, q_stride, out, out_stride, scratch, kc, vc, block_table, bt_stride, cu_q, q_start,
-                                        requests, nq, nkv, d, ps, num_pages, scale, window, splits, nullptr, 0, status, stream);
+                                        requests, nq, nkv, d, ps, num_pages, scale, window, 0, splits, nullptr, 0, status, stream);
 }
 
 extern "C" int fe_paged_prefill_mma(const void* q, long long q_stride, void* out, long long out_stride,
                                     const void* kc, const void* vc, const int* block_table, int bt_stride,
                                     const int* cu_q, const int* q_start, int requests, int max_q_len, int nq, int nkv,
-                                    int d, int ps, int num_pages, float scale, int window, int* status,
+                                    int d, int ps, int num_pages, float scale, int window, int sink, int* status,
                                     cudaStream_t stream) {
     if (check_common("paged_prefill", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
     FE_REQUIRE(requests >= 0 && max_q_len >= 0, "paged_prefill: bad request count or length");
@@ -829,7 +839,7 @@ extern "C" int fe_paged_prefill_mma(const void* q, long long q_stride, void* out
         if (allow_smem(paged_prefill_kernel<DMAX>, prefill_smem<DMAX>(), "paged_prefill")) return 1;           \
         fe::launch(paged_prefill_kernel<DMAX>, grid, PREFILL_WARPS * 32, prefill_smem<DMAX>(), stream,                 \
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kc, (const bf16*)vc, block_table,  \
-            bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, status);                  \
+            bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, sink, status);            \
     } while (0)
     if (d <= 64) FE_PREFILL(64);
     else if (d <= 128) FE_PREFILL(128);

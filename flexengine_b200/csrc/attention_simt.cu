@@ -4,7 +4,9 @@
 // position 0, one key per lane; scores, running maximum, running sum and the value accumulator
 // are float (online softmax, as the reference's block-wise path:
 // inference/attention/paged.py:50-70).  Key t is visible to the query at position p iff t <= p
-// (and t > p - window when window > 0) (paged.py:31-32).  Query head h reads key/value head
+// (and t > p - window when window > 0; t in the chunk of -window positions that holds p when window < 0)
+// (paged.py:31-32).  ``sink``: the softmax starts as if a key of score 0 and value 0 had been seen, which adds
+// 1 to its denominator.  Query head h reads key/value head
 // h / (nq / nkv) (paged.py:29-30).  Because the blocks are aligned to position 0 and taken in
 // order, the result for a query does not depend on how its request was cut into steps.
 //
@@ -23,7 +25,7 @@ __global__ void paged_attention_simt_kernel(const T* __restrict__ q, long long q
                                             int bt_stride, const int* __restrict__ cu_q,
                                             const int* __restrict__ q_start, const int* __restrict__ token_req,
                                             int T_tokens, int nq, int nkv, int d, int ps, int num_pages, float scale,
-                                            int window, int* __restrict__ status) {
+                                            int window, int sink, int* __restrict__ status) {
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ float q_smem[];
@@ -40,12 +42,12 @@ __global__ void paged_attention_simt_kernel(const T* __restrict__ q, long long q
     for (int j = lane; j < d; j += 32) qs[j] = to_float(qp[j]);
     __syncwarp();
 
-    float m = -CUDART_INF_F, l = 0.f;
+    float m = sink ? 0.f : -CUDART_INF_F, l = sink ? 1.f : 0.f;
     float acc[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
 
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = first_visible(pos, window);
     const int* table = block_table + (size_t)r * bt_stride;
     for (int kb = (lo / 32) * 32; kb <= pos; kb += 32) {
         const int t = kb + lane;
@@ -106,7 +108,7 @@ template <typename T>
 static int launch_simt(const void* q, long long q_stride, void* out, long long out_stride, const void* kc,
                        const void* vc, const int* block_table, int bt_stride, const int* cu_q, const int* q_start,
                        const int* token_req, int T_tokens, int nq, int nkv, int d, int ps, int num_pages,
-                       float scale, int window, int* status, cudaStream_t stream) {
+                       float scale, int window, int sink, int* status, cudaStream_t stream) {
     const int warps = 4;
     const long long total = (long long)T_tokens * nq;
     const int blocks = (int)((total + warps - 1) / warps);
@@ -114,7 +116,7 @@ static int launch_simt(const void* q, long long q_stride, void* out, long long o
 #define FE_LAUNCH_SIMT(DPL)                                                                                      \
     fe::launch(paged_attention_simt_kernel<T, DPL>, blocks, warps * 32, smem, stream,                                    \
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kc, (const T*)vc, block_table, bt_stride, cu_q,   \
-        q_start, token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, status)
+        q_start, token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, sink, status)
     if (d <= 32) FE_LAUNCH_SIMT(1);
     else if (d <= 64) FE_LAUNCH_SIMT(2);
     else if (d <= 128) FE_LAUNCH_SIMT(4);
@@ -129,17 +131,17 @@ extern "C" int fe_paged_attention_simt(const void* q, long long q_stride, void* 
                                        const void* kc, const void* vc, const int* block_table, int bt_stride,
                                        const int* cu_q, const int* q_start, const int* token_req, int T_tokens,
                                        int nq, int nkv, int d, int ps, int num_pages, float scale, int window,
-                                       int dtype, int* status, cudaStream_t stream) {
+                                       int sink, int dtype, int* status, cudaStream_t stream) {
     FE_REQUIRE(T_tokens >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "paged_attention: bad head counts %d/%d", nq, nkv);
     FE_REQUIRE(d >= 16 && d <= 1024 && d % 16 == 0, "paged_attention: head size %d is not a multiple of 16 in [16, 1024]", d);
-    FE_REQUIRE(ps > 0 && num_pages > 0 && window >= 0, "paged_attention: bad page size, page count or window");
+    FE_REQUIRE(ps > 0 && num_pages > 0, "paged_attention: bad page size or page count");
     FE_REQUIRE(q_stride % 8 == 0, "paged_attention: query row stride %lld must be a multiple of 8 elements", q_stride);
     if (T_tokens == 0) return 0;
     if (dtype == FE_F32)
         return launch_simt<float>(q, q_stride, out, out_stride, kc, vc, block_table, bt_stride, cu_q, q_start,
-                                  token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, status, stream);
+                                  token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, sink, status, stream);
     if (dtype == FE_BF16)
         return launch_simt<bf16>(q, q_stride, out, out_stride, kc, vc, block_table, bt_stride, cu_q, q_start,
-                                 token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, status, stream);
+                                 token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, sink, status, stream);
     FE_REQUIRE(false, "paged_attention: unknown dtype %d", dtype);
 }

@@ -2,7 +2,8 @@
 //
 // Math as the reference's block-wise path (inference/attention/paged.py:50-70): scores
 // q.k / sqrt(d), key t visible to the query at position p iff t <= p (and t > p - window when
-// window > 0), running maximum / sum / output in float (online softmax), query head h reads
+// window > 0; t in the chunk of -window positions that holds p when window < 0; with ``sink`` the softmax of a row
+// starts as if a key of score 0 and value 0 had been seen, in the first split of its keys), running maximum / sum / output in float (online softmax), query head h reads
 // key/value head h / (nq / nkv).
 //
 // A block takes 256 rows of one (request, key/value head) as two tiles of 128: row m is the pair
@@ -236,7 +237,7 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
                              const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                              const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q,
                              const int* __restrict__ q_start, int nq, int nkv, int ps, int num_pages, float scale_log2,
-                             int window, int splits, float* __restrict__ part_o, float* __restrict__ part_lse,
+                             int window, int sink, int splits, float* __restrict__ part_o, float* __restrict__ part_lse,
                              int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long kv_full[KV_STAGES], kv_empty[KV_STAGES], s_ready[2][2], p_ready[2][2], pv_done[2], o_final[2];
@@ -267,7 +268,7 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
     // keys this block needs: from the window edge of its first query to its last query
     const int qi_first = m_pair / G, qi_last = min(n_q - 1, (m_pair + (two ? 2 : 1) * ROWS - 1) / G);
     const int hi = start + qi_last;
-    const int lo = window > 0 ? max(0, start + qi_first - window + 1) : 0;
+    const int lo = first_visible(start + qi_first, window);
     // this block's share of the key tiles; with one split, all of them
     const int all_tiles = hi / KEYS - lo / KEYS + 1, per_split = (all_tiles + splits - 1) / splits;
     const int t_begin = lo / KEYS + split * per_split, n_tiles = min(per_split, all_tiles - split * per_split);
@@ -301,7 +302,7 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
     const bool valid = softmax_thread && m < rows;
     const int qi = valid ? m / G : 0, head = kvh * G + (valid ? m % G : 0);
     const int pos = valid ? start + qi : -1;
-    const int row_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int row_lo = first_visible(pos, window);
     // where this thread's row starts in q and in out (in elements); other lanes fetch it by shuffle
     const long long q_off = valid ? (long long)(tok0 + qi) * q_stride + (long long)head * D : -1;
     const long long out_off = valid ? (long long)(tok0 + qi) * out_stride + (long long)head * D : -1;
@@ -428,6 +429,7 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
         const unsigned o_addr = tmem_base + lane_bits + 256 + ti * 128;
         const int pos_min = __reduce_min_sync(FULL, pos), lo_max = __reduce_max_sync(FULL, row_lo);
         float m_ref = -CUDART_INF_F, row_sum = 0.f;
+        if (sink && split == 0) { m_ref = 0.f; row_sum = 1.f; }
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             ok = __all_sync(FULL, mbar_wait(&s_ready[ti][j & 1], (j >> 1) & 1, &give_up));
@@ -448,11 +450,11 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
             if (__any_sync(FULL, m_new > m_ref + RESCALE_STEP)) {
                 // move the reference point to the new maximum: O and the sum were taken against the old one
                 const float alpha = m_new == -CUDART_INF_F ? 1.f : ex2(m_ref - m_new);
+                row_sum *= alpha;                                  // not zero before the first tile when a sink started it
                 if (j > 0) {
                     ok = __all_sync(FULL, mbar_wait(&pv_done[ti], (j - 1) & 1, &give_up));      // O_i is at rest
                     if (!ok) break;
                     tc_fence_after();
-                    row_sum *= alpha;
 #pragma unroll 1
                     for (int c = 0; c < D; c += 32) {
                         float v[32];
@@ -573,7 +575,7 @@ prefill_merge_kernel(const float* __restrict__ part_o, const float* __restrict__
 template <int D>
 int launch(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
            const int* block_table, int bt_stride, const int* cu_q, const int* q_start, int requests, int max_q_len, int nq,
-           int nkv, int ps, int num_pages, float scale, int window, int splits, float* scratch, long long total_tokens,
+           int nkv, int ps, int num_pages, float scale, int window, int sink, int splits, float* scratch, long long total_tokens,
            int* status, cudaStream_t stream) {
     const size_t smem = (size_t)(D / 64) * (2 * Q_BLOCK + 2 * KV_STAGES * KV_BLOCK) + 1024;
     const cudaError_t err = cudaFuncSetAttribute(paged_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -586,7 +588,7 @@ int launch(const void* q, long long q_stride, void* out, long long out_stride, c
     float* part_lse = splits > 1 ? scratch + (size_t)total_tokens * nq * splits * D : nullptr;
     fe::launch(paged_prefill_tcgen05_kernel<D>, dim3((unsigned)tiles, nkv, requests), THREADS, smem, stream, (const bf16*)q, q_stride,
                (bf16*)out, out_stride, (const bf16*)kc, (const bf16*)vc, block_table, bt_stride, cu_q, q_start, nq, nkv, ps,
-               num_pages, scale * LOG2E, window, splits, part_o, part_lse, status);
+               num_pages, scale * LOG2E, window, sink, splits, part_o, part_lse, status);
     if (fe_check_launch("paged_prefill_tcgen05")) return 1;
     if (splits > 1) {
         const long long items = total_tokens * nq;
@@ -611,11 +613,11 @@ extern "C" long long fe_paged_prefill_tcgen05_scratch_floats(long long total_tok
 extern "C" int fe_paged_prefill_tcgen05(const void* q, long long q_stride, void* out, long long out_stride, const void* kc,
                                         const void* vc, const int* block_table, int bt_stride, const int* cu_q,
                                         const int* q_start, int requests, int max_q_len, int nq, int nkv, int d, int ps,
-                                        int num_pages, float scale, int window, int splits, void* scratch,
+                                        int num_pages, float scale, int window, int sink, int splits, void* scratch,
                                         long long total_tokens, int* status, cudaStream_t stream) {
     FE_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "paged_prefill_tcgen05: bad head counts %d/%d", nq, nkv);
     FE_REQUIRE(d == 64 || d == 128, "paged_prefill_tcgen05: head size %d; this kernel takes 64 and 128", d);
-    FE_REQUIRE(ps > 0 && num_pages > 0 && window >= 0, "paged_prefill_tcgen05: bad page size, page count or window");
+    FE_REQUIRE(ps > 0 && num_pages > 0, "paged_prefill_tcgen05: bad page size or page count");
     FE_REQUIRE(q_stride % 8 == 0 && out_stride % 8 == 0 && (((size_t)q | (size_t)out | (size_t)kc | (size_t)vc) & 15) == 0,
                "paged_prefill_tcgen05: rows must start on 16-byte boundaries");
     FE_REQUIRE(requests >= 0 && max_q_len >= 0, "paged_prefill_tcgen05: bad request count or length");
@@ -625,7 +627,7 @@ extern "C" int fe_paged_prefill_tcgen05(const void* q, long long q_stride, void*
     if (requests == 0 || max_q_len == 0) return 0;
     if (d == 64)
         return launch<64>(q, q_stride, out, out_stride, kc, vc, block_table, bt_stride, cu_q, q_start, requests, max_q_len, nq, nkv,
-                          ps, num_pages, scale, window, splits, (float*)scratch, total_tokens, status, stream);
+                          ps, num_pages, scale, window, sink, splits, (float*)scratch, total_tokens, status, stream);
     return launch<128>(q, q_stride, out, out_stride, kc, vc, block_table, bt_stride, cu_q, q_start, requests, max_q_len, nq, nkv, ps,
-                       num_pages, scale, window, splits, (float*)scratch, total_tokens, status, stream);
+                       num_pages, scale, window, sink, splits, (float*)scratch, total_tokens, status, stream);
 }

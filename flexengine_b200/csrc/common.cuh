@@ -93,6 +93,14 @@ template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float* v
     *reinterpret_cast<uint4*>(p) = raw;
 }
 
+// What a query at position ``pos`` sees of the keys t <= pos, as one int: 0 every key; w > 0 the last w keys (a sliding
+// window); -c < 0 the keys of its own chunk of c positions, counted from position 0.  The first visible key:
+__host__ __device__ __forceinline__ int first_visible(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0 && pos > 0) return pos - pos % (-window);
+    return 0;
+}
+
 // Programmatic dependent launch: a kernel launched through fe::launch may begin while the kernel
 // before it in the stream is still running.  Everything it reads that an earlier kernel wrote,
 // and every write, must come after griddep_wait(); only data that no kernel writes (weights)

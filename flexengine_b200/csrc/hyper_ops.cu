@@ -1,0 +1,585 @@
+// Kernels of decoders that keep several residual streams and of the mixers such designs bring along:
+//   embedding into S copies of the stream, scaled;
+//   the norm that reads a learned sum of the streams, with the sublayer before written into them in the same pass;
+//   token shift (a row blended with the row of the token before, kept per request between steps);
+//   what attention does between its projection and its scores: a short causal convolution over time with a kept history,
+//     rotation of part of every head, unit norm of queries and keys, the cache write, all padded to one head size;
+//   per-head output gates; the minGRU recurrence; a gated activation with a choice of gate function.
+// All arithmetic is float; exp, tanh, sine, cosine and rsqrt are the accurate library forms.
+#define FE_PDL_CLASS 4      // FE_PDL_ELEMENTWISE
+#include "common.cuh"
+
+using namespace fe;
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + expf(-x)); }
+
+constexpr int MAX_STREAMS = 16;
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// out[s, t, :] = table[ids[t], :] * scale for every stream s.
+template <typename T>
+__global__ void embedding_streams_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
+                                         int T_tokens, int H, int V, float scale, int streams, int* __restrict__ status) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool bad = id < 0 || id >= V;
+    if (bad && threadIdx.x == 0 && status) atomicOr(status, FE_STATUS_BAD_TOKEN);
+    const T* row = table + (size_t)(bad ? 0 : id) * H;
+    const size_t plane = (size_t)T_tokens * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float v = bad ? 0.f : to_float(row[j]) * scale;
+        for (int s = 0; s < streams; ++s) out[s * plane + (size_t)t * H + j] = v;
+    }
+}
+
+extern "C" int fe_embedding_streams(const int* ids, const void* table, float* out, int T, int H, int V, float scale, int streams,
+                                    int dtype, int* status, cudaStream_t stream) {
+    FE_REQUIRE(T >= 0 && H > 0 && V > 0 && streams >= 1, "embedding_streams: bad sizes T=%d H=%d V=%d streams=%d", T, H, V, streams);
+    if (T == 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == FE_F32)
+        fe::launch(embedding_streams_kernel<float>, T, threads, 0, stream, ids, (const float*)table, out, T, H, V, scale, streams, status);
+    else if (dtype == FE_BF16)
+        fe::launch(embedding_streams_kernel<bf16>, T, threads, 0, stream, ids, (const bf16*)table, out, T, H, V, scale, streams, status);
+    else
+        FE_REQUIRE(false, "embedding_streams: unknown dtype %d", dtype);
+    return fe_check_launch("embedding_streams");
+}
+
+// ---------------------------------------------------------------------------------------------
+// One block per output row.  x [S, T, H] float.  If y is given, the sublayer before is put into the streams first:
+//   x_t <- sum_s mix[s, t] x_s + write[t] * y * sigmoid(gate + gate_bias)         (every stream from the old ones)
+// then u = sum_s read[s] x_s (read null: the plain sum), out = u * rsqrt(mean(u^2) + eps) * weight.
+// rows == nullptr: row i, and the new streams are written back; rows != nullptr: output row i reads row rows[i] and the
+// streams are left as they are.  u is staged in shared memory (H floats).
+template <typename T, int SMAX>
+__global__ void stream_rmsnorm_kernel(float* __restrict__ x, int S, int T_tokens, int H, const float* __restrict__ read,
+                                      const float* __restrict__ weight, float eps, const T* __restrict__ y,
+                                      const T* __restrict__ gate, const float* __restrict__ gate_bias,
+                                      const float* __restrict__ mix, const float* __restrict__ write,
+                                      const int* __restrict__ rows, T* __restrict__ out) {
+    griddep_wait();
+    griddep_launch_dependents();
+    extern __shared__ float u_row[];
+    __shared__ float scratch[33];
+    __shared__ float s_mix[SMAX * SMAX], s_write[SMAX], s_read[SMAX];
+    for (int e = threadIdx.x; e < S * S; e += blockDim.x) s_mix[e] = mix ? mix[e] : 0.f;
+    for (int e = threadIdx.x; e < S; e += blockDim.x) {
+        s_write[e] = write ? write[e] : 0.f;
+        s_read[e] = read ? read[e] : 1.f;
+    }
+    __syncthreads();
+    const int i = blockIdx.x;
+    int r = rows ? rows[i] : i;
+    if (r < 0 || r >= T_tokens) r = 0;              // guarded: rows are checked on the host
+    const size_t plane = (size_t)T_tokens * H;
+    float* base = x + (size_t)r * H;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v[SMAX];
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s) v[s] = s < S ? base[s * plane + j] : 0.f;
+        float u = 0.f;
+        if (y) {
+            const float g = to_float(y[(size_t)r * H + j]) * sigmoidf(to_float(gate[(size_t)r * H + j]) + gate_bias[j]);
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t) {
+                if (t < S) {
+                    float n = 0.f;
+#pragma unroll
+                    for (int s = 0; s < SMAX; ++s)
+                        if (s < S) n = fmaf(s_mix[s * S + t], v[s], n);
+                    n = fmaf(s_write[t], g, n);
+                    if (!rows) base[t * plane + j] = n;
+                    u = fmaf(s_read[t], n, u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < SMAX; ++s)
+                if (s < S) u = fmaf(s_read[s], v[s], u);
+        }
+        u_row[j] = u;
+        ss += u * u;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)H + eps);
+    T* o = out + (size_t)i * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_float<T>(u_row[j] * inv * weight[j]);
+}
+
+template <typename T>
+static int launch_stream_rmsnorm(float* x, int S, int T_tokens, int H, const float* read, const float* weight, float eps, const void* y,
+                                 const void* gate, const float* gate_bias, const float* mix, const float* write, const int* rows,
+                                 int n_out, void* out, cudaStream_t stream) {
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const size_t smem = (size_t)H * sizeof(float);
+#define FE_LAUNCH_STREAM_NORM(SMAX)                                                                                       \
+    fe::launch(stream_rmsnorm_kernel<T, SMAX>, n_out, threads, smem, stream, x, S, T_tokens, H, read, weight, eps,       \
+               (const T*)y, (const T*)gate, gate_bias, mix, write, rows, (T*)out)
+    if (S <= 1) FE_LAUNCH_STREAM_NORM(1);
+    else if (S <= 2) FE_LAUNCH_STREAM_NORM(2);
+    else if (S <= 4) FE_LAUNCH_STREAM_NORM(4);
+    else if (S <= 8) FE_LAUNCH_STREAM_NORM(8);
+    else FE_LAUNCH_STREAM_NORM(16);
+#undef FE_LAUNCH_STREAM_NORM
+    return fe_check_launch("stream_rmsnorm");
+}
+
+extern "C" int fe_stream_rmsnorm(float* x, int S, int T, int H, const float* read, const float* weight, float eps, const void* y,
+                                 const void* gate, const float* gate_bias, const float* mix, const float* write, const int* rows,
+                                 int n_out, void* out, int dtype, cudaStream_t stream) {
+    FE_REQUIRE(S >= 1 && S <= MAX_STREAMS && T >= 0 && H > 0 && n_out >= 0, "stream_rmsnorm: bad sizes S=%d T=%d H=%d", S, T, H);
+    FE_REQUIRE((size_t)H * sizeof(float) <= 48 * 1024, "stream_rmsnorm: rows of %d floats do not fit shared memory", H);
+    FE_REQUIRE(y == nullptr || (gate && gate_bias && mix && write), "stream_rmsnorm: an update needs its gate, bias, mix and write");
+    if (n_out == 0 || T == 0) return 0;
+    if (dtype == FE_F32)
+        return launch_stream_rmsnorm<float>(x, S, T, H, read, weight, eps, y, gate, gate_bias, mix, write, rows, n_out, out, stream);
+    if (dtype == FE_BF16)
+        return launch_stream_rmsnorm<bf16>(x, S, T, H, read, weight, eps, y, gate, gate_bias, mix, write, rows, n_out, out, stream);
+    FE_REQUIRE(false, "stream_rmsnorm: unknown dtype %d", dtype);
+}
+
+// ---------------------------------------------------------------------------------------------
+// out = h + (h' - h) * mu, h' the row of the token before.  A request's first token of the step takes the row its seat
+// kept (``kept`` [seats, stride] float; zeros for a seat below 0), and the thread that read it writes the request's last
+// row of this step in its place, element by element, so nobody else touches it.
+template <typename T>
+__global__ void token_shift_kernel(const T* __restrict__ h, const float* __restrict__ mu, float* kept, long long kept_stride,
+                                   const int* __restrict__ seats, const int* __restrict__ cu_q, const int* __restrict__ token_req,
+                                   T* __restrict__ out, int D, int n_seats) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int t = blockIdx.x;
+    const int r = token_req[t];
+    const int first = cu_q[r];
+    const int seat = seats[r];
+    float* mine = (seat >= 0 && seat < n_seats) ? kept + (size_t)seat * kept_stride : nullptr;
+    const T* row = h + (size_t)t * D;
+    const T* prev = t > first ? h + (size_t)(t - 1) * D : nullptr;
+    const T* last = h + (size_t)(cu_q[r + 1] - 1) * D;
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < D; j += gridDim.y * blockDim.x) {
+        const float x = to_float(row[j]);
+        float before = 0.f;
+        if (prev) before = to_float(prev[j]);
+        else if (mine) {
+            before = mine[j];
+            mine[j] = to_float(last[j]);
+        }
+        out[(size_t)t * D + j] = from_float<T>(fmaf(before - x, mu[j], x));
+    }
+}
+
+extern "C" int fe_token_shift(const void* h, const float* mu, float* kept, long long kept_stride, const int* seats, const int* cu_q,
+                              const int* token_req, void* out, int T, int D, int n_seats, int dtype, cudaStream_t stream) {
+    FE_REQUIRE(T >= 0 && D > 0 && n_seats >= 0 && kept_stride >= D, "token_shift: bad sizes");
+    if (T == 0) return 0;
+    const int threads = D >= 1024 ? 256 : 128;
+    const int stretches = T >= 512 ? 1 : (D + threads - 1) / threads;
+    const dim3 grid(T, stretches < 65535 ? stretches : 65535);
+    if (dtype == FE_F32)
+        fe::launch(token_shift_kernel<float>, grid, threads, 0, stream, (const float*)h, mu, kept, kept_stride, seats, cu_q, token_req,
+                   (float*)out, D, n_seats);
+    else if (dtype == FE_BF16)
+        fe::launch(token_shift_kernel<bf16>, grid, threads, 0, stream, (const bf16*)h, mu, kept, kept_stride, seats, cu_q, token_req,
+                   (bf16*)out, D, n_seats);
+    else
+        FE_REQUIRE(false, "token_shift: unknown dtype %d", dtype);
+    return fe_check_launch("token_shift");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Between the projection and the scores.  ``proj`` [T, ld] holds q | k | v of every token: ``heads`` query heads and
+// ``kv_heads`` key heads of ``dim`` entries, ``kv_heads`` value heads of ``vdim``.  One warp per (token, head of q, k or v):
+//   convolution (taps > 0): y_t[c] = sum_j conv[c, j] * u_(t - taps + 1 + j)[c] over the request's own rows, those before
+//     this step from ``history`` [seats, (taps - 1) * C] (oldest first; zeros for a seat below 0);
+//   rotation (q, k): entries i and i + rot/2 of the head's first ``rot`` turn by position * inv_freq[i];
+//   unit norm (q, k; qk_norm): the head divided by sqrt(mean of its squares + eps);
+//   q into ``q_out`` [T, heads * head], k and v into their cache slots [pages, kv_heads, ps, head], zeros beyond dim / vdim.
+// The history of a channel is read only by the first taps - 1 tokens of the request's portion.  The warp of the portion's
+// first token therefore runs all of them for its head, one after the other, and then brings the history of its channels up to
+// date (the warps of the other early tokens do nothing), so that no warp reads what another one writes.
+template <typename T>
+__global__ void qkv_conv_rope_norm_cache_kernel(const T* __restrict__ proj, long long ld, const float* __restrict__ conv, float* history,
+                                                long long history_stride, int taps, const int* __restrict__ seats,
+                                                const int* __restrict__ cu_q, const int* __restrict__ token_req,
+                                                const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot,
+                                                int qk_norm, float eps, const int* __restrict__ slot_mapping, T* __restrict__ kc,
+                                                T* __restrict__ vc, T* __restrict__ q_out, int T_tokens, int heads, int kv_heads, int dim,
+                                                int vdim, int head, int ps, long long num_slots, int n_seats, int* __restrict__ status) {
+    griddep_wait();
+    griddep_launch_dependents();
+    extern __shared__ float staged[];
+    const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
+    const int per_token = heads + 2 * kv_heads;
+    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + warp_in_block;
+    if (warp >= (long long)T_tokens * per_token) return;
+    const int tok = (int)(warp / per_token), hs = (int)(warp % per_token);
+    float* buf = staged + (size_t)warp_in_block * head;
+    const int C = (heads + kv_heads) * dim + kv_heads * vdim;
+    // which head this is: 0 query, 1 key, 2 value; its first channel and its size
+    const int what = hs < heads ? 0 : (hs < heads + kv_heads ? 1 : 2);
+    const int index = what == 0 ? hs : (what == 1 ? hs - heads : hs - heads - kv_heads);
+    const int hd = what == 2 ? vdim : dim;
+    const int ch0 = what == 0 ? index * dim : (what == 1 ? (heads + index) * dim : (heads + kv_heads) * dim + index * vdim);
+    const int r = token_req[tok];
+    const int first = cu_q[r], n = cu_q[r + 1] - first, li = tok - first;
+    const int seat = seats[r];
+    const int back = taps > 1 ? taps - 1 : 0;
+    float* hist = (back && history && seat >= 0 && seat < n_seats) ? history + (size_t)seat * history_stride : nullptr;
+    int reps = 1;
+    if (back) {
+        if (li == 0) reps = min(n, back);
+        else if (li < back) return;
+    }
+    for (int rep = 0; rep < reps; ++rep) {
+        const int t = tok + rep, lt = li + rep;
+        for (int c = lane; c < hd; c += 32) {
+            const int ch = ch0 + c;
+            float acc;
+            if (conv) {
+                acc = 0.f;
+                for (int j = 0; j < taps; ++j) {
+                    const int from = lt - (taps - 1 - j);
+                    float u = 0.f;
+                    if (from >= 0) u = to_float(proj[(size_t)(first + from) * ld + ch]);
+                    else if (hist) u = hist[(size_t)(back + from) * C + ch];
+                    acc = fmaf(conv[(size_t)ch * taps + j], u, acc);
+                }
+            } else {
+                acc = to_float(proj[(size_t)t * ld + ch]);
+            }
+            buf[c] = acc;
+        }
+        __syncwarp();
+        float inv = 1.f;
+        if (what != 2) {
+            if (inv_freq && rot > 0) {
+                const float pos = (float)positions[t];
+                const int half = rot >> 1;
+                for (int i = lane; i < half; i += 32) {
+                    float s, c;
+                    sincosf(pos * inv_freq[i], &s, &c);
+                    const float a = buf[i], b = buf[i + half];
+                    buf[i] = a * c - b * s;
+                    buf[i + half] = b * c + a * s;
+                }
+                __syncwarp();
+            }
+            if (qk_norm) {
+                float ss = 0.f;
+                for (int c = lane; c < hd; c += 32) ss = fmaf(buf[c], buf[c], ss);
+                ss = warp_sum(ss);
+                inv = rsqrtf(ss / (float)hd + eps);
+            }
+        }
+        T* dst = nullptr;
+        if (what == 0) {
+            dst = q_out + (size_t)t * heads * head + (size_t)index * head;
+        } else if (slot_mapping) {
+            const int slot = slot_mapping[t];
+            if (slot >= 0) {
+                if (slot >= num_slots) {
+                    if (lane == 0 && status) atomicOr(status, FE_STATUS_BAD_SLOT);
+                } else {
+                    const long long page = slot / ps, off = slot % ps;
+                    dst = (what == 1 ? kc : vc) + ((page * kv_heads + index) * ps + off) * head;
+                }
+            }
+        }
+        if (dst)
+            for (int c = lane; c < head; c += 32) dst[c] = from_float<T>(c < hd ? buf[c] * inv : 0.f);
+        __syncwarp();
+    }
+    if (hist && li == 0) {
+        // the last ``back`` projected rows of the request, oldest first: what was kept moves up, this step's rows follow
+        for (int c = lane; c < hd; c += 32) {
+            const int ch = ch0 + c;
+            for (int m = 0; m < back; ++m) {
+                const int from = m + n;
+                hist[(size_t)m * C + ch] = from < back ? hist[(size_t)from * C + ch] : to_float(proj[(size_t)(first + from - back) * ld + ch]);
+            }
+        }
+    }
+}
+
+extern "C" int fe_qkv_conv_rope_norm_cache(const void* proj, long long ld, const float* conv, float* history, long long history_stride,
+                                           int taps, const int* seats, const int* cu_q, const int* token_req, const int* positions,
+                                           const float* inv_freq, int rot, int qk_norm, float eps, const int* slot_mapping, void* kc,
+                                           void* vc, void* q_out, int T, int heads, int kv_heads, int dim, int vdim, int head, int ps,
+                                           long long num_slots, int n_seats, int dtype, int* status, cudaStream_t stream) {
+    FE_REQUIRE(T >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && head >= dim && head >= vdim && head <= 1024,
+               "qkv_conv_rope_norm_cache: bad sizes heads=%d kv_heads=%d dim=%d vdim=%d head=%d", heads, kv_heads, dim, vdim, head);
+    FE_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dim && ps > 0 && taps >= 0, "qkv_conv_rope_norm_cache: bad rotation, page size or taps");
+    FE_REQUIRE(conv != nullptr || taps == 0, "qkv_conv_rope_norm_cache: taps without a table");
+    FE_REQUIRE(taps <= 1 || history != nullptr, "qkv_conv_rope_norm_cache: a convolution of several taps needs its history");
+    const long long C = (long long)(heads + kv_heads) * dim + (long long)kv_heads * vdim;
+    FE_REQUIRE(ld >= C && (taps <= 1 || history_stride >= (taps - 1) * C), "qkv_conv_rope_norm_cache: rows too short");
+    if (T == 0) return 0;
+    const int warps = 4;
+    const long long total = (long long)T * (heads + 2 * kv_heads);
+    const long long blocks = (total + warps - 1) / warps;
+    FE_REQUIRE(blocks <= 2147483647LL, "qkv_conv_rope_norm_cache: grid too large");
+    const size_t smem = (size_t)warps * head * sizeof(float);
+    if (dtype == FE_F32)
+        fe::launch(qkv_conv_rope_norm_cache_kernel<float>, (unsigned)blocks, warps * 32, smem, stream, (const float*)proj, ld, conv, history,
+                   history_stride, taps, seats, cu_q, token_req, positions, inv_freq, rot, qk_norm, eps, slot_mapping, (float*)kc,
+                   (float*)vc, (float*)q_out, T, heads, kv_heads, dim, vdim, head, ps, num_slots, n_seats, status);
+    else if (dtype == FE_BF16)
+        fe::launch(qkv_conv_rope_norm_cache_kernel<bf16>, (unsigned)blocks, warps * 32, smem, stream, (const bf16*)proj, ld, conv, history,
+                   history_stride, taps, seats, cu_q, token_req, positions, inv_freq, rot, qk_norm, eps, slot_mapping, (bf16*)kc,
+                   (bf16*)vc, (bf16*)q_out, T, heads, kv_heads, dim, vdim, head, ps, num_slots, n_seats, status);
+    else
+        FE_REQUIRE(false, "qkv_conv_rope_norm_cache: unknown dtype %d", dtype);
+    return fe_check_launch("qkv_conv_rope_norm_cache");
+}
+
+// ---------------------------------------------------------------------------------------------
+// out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(gates[t * ld + h]): every head's output times its gate, the padding of
+// the attention kernels' head size dropped on the way.
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ mixed, const T* __restrict__ gates, long long ld, T* __restrict__ out,
+                                 long long total, int heads, int head, int vdim) {
+    griddep_wait();
+    griddep_launch_dependents();
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(e % vdim);
+        const long long th = e / vdim;
+        const int h = (int)(th % heads);
+        const long long t = th / heads;
+        out[e] = from_float<T>(to_float(mixed[(t * heads + h) * head + c]) * sigmoidf(to_float(gates[t * ld + h])));
+    }
+}
+
+extern "C" int fe_head_gate(const void* mixed, const void* gates, long long ld, void* out, int T, int heads, int head, int vdim,
+                            int dtype, cudaStream_t stream) {
+    FE_REQUIRE(T >= 0 && heads > 0 && head >= vdim && vdim > 0, "head_gate: bad sizes");
+    const long long total = (long long)T * heads * vdim;
+    if (total == 0) return 0;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 65535LL * 4 ? want : 65535LL * 4);
+    if (dtype == FE_F32)
+        fe::launch(head_gate_kernel<float>, blocks, 256, 0, stream, (const float*)mixed, (const float*)gates, ld, (float*)out, total, heads,
+                   head, vdim);
+    else if (dtype == FE_BF16)
+        fe::launch(head_gate_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)mixed, (const bf16*)gates, ld, (bf16*)out, total, heads,
+                   head, vdim);
+    else
+        FE_REQUIRE(false, "head_gate: unknown dtype %d", dtype);
+    return fe_check_launch("head_gate");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The minGRU recurrence.  zxg [T, 3 W] float holds, per token, the projections of the gate, the candidate and the output
+// gate before their biases and activations:
+//   z = sigmoid(zxg[:, c] + bias[c]);  u = zxg[:, W + c] + bias[W + c];  cand = u >= 0 ? u + 1/2 : sigmoid(u);
+//   S <- (1 - z) S + z cand;   out = S * silu(zxg[:, 2 W + c]).
+// S of a request lives in state[seat, :W] (zeros and nothing kept for a seat below 0).
+namespace {
+
+struct GruStep { float a, b; };      // S <- a S + b
+
+__device__ __forceinline__ GruStep gru_step(float zl, float xl, float bz, float bx) {
+    const float z = sigmoidf(zl + bz);
+    const float u = xl + bx;
+    const float cand = u >= 0.f ? u + 0.5f : sigmoidf(u);
+    return GruStep{1.f - z, z * cand};
+}
+__device__ __forceinline__ float silu(float g) { return g / (1.f + expf(-g)); }
+
+constexpr int GRU_AHEAD = 8;         // tokens whose values are asked for together: the chain of S waits for memory once per 8
+
+}  // namespace
+
+// One thread per (request, channel) walks the request's tokens in order.
+template <typename T>
+__global__ void mingru_walk_kernel(const float* __restrict__ zxg, const float* __restrict__ bias, float* state, long long state_stride,
+                                   const int* __restrict__ seats, const int* __restrict__ cu_q, T* __restrict__ out, int W, int n_seats) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    const int r = blockIdx.y;
+    const int seat = seats[r];
+    float* mine = (seat >= 0 && seat < n_seats) ? state + (size_t)seat * state_stride : nullptr;
+    float S = mine ? mine[c] : 0.f;
+    const float bz = bias[c], bx = bias[W + c];
+    const int begin = cu_q[r], end = cu_q[r + 1];
+    const size_t ld = (size_t)3 * W;
+    for (int t0 = begin; t0 < end; t0 += GRU_AHEAD) {
+        float zl[GRU_AHEAD], xl[GRU_AHEAD], gl[GRU_AHEAD];
+#pragma unroll
+        for (int i = 0; i < GRU_AHEAD; ++i) {
+            const int t = min(t0 + i, end - 1);
+            zl[i] = zxg[t * ld + c]; xl[i] = zxg[t * ld + W + c]; gl[i] = zxg[t * ld + 2 * W + c];
+        }
+#pragma unroll
+        for (int i = 0; i < GRU_AHEAD; ++i) {
+            if (t0 + i < end) {
+                const GruStep s = gru_step(zl[i], xl[i], bz, bx);
+                S = fmaf(s.a, S, s.b);
+                out[(size_t)(t0 + i) * W + c] = from_float<T>(S * silu(gl[i]));
+            }
+        }
+    }
+    if (mine) mine[c] = S;
+}
+
+// Long portions: the recurrence is linear in S, so a request's tokens are cut into blocks of ``span``.  The first kernel
+// folds every block into (A, B) with S_end = A S_begin + B and copies the kept state aside; the second starts every block
+// from the S that the blocks before it give (folded in order from that copy), walks it and writes the outputs; the last
+// block keeps S.  Scratch per request: [max_blocks][A | B][W], then the copy of the kept state [W].
+__global__ void mingru_fold_kernel(const float* __restrict__ zxg, const float* __restrict__ bias, const float* __restrict__ state,
+                                   long long state_stride, const int* __restrict__ seats, const int* __restrict__ cu_q,
+                                   float* __restrict__ folds, int W, int span, int max_blocks, int n_seats) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    const int r = blockIdx.z, blk = blockIdx.y;
+    const int begin = cu_q[r] + blk * span, end = min(cu_q[r + 1], begin + span);
+    if (blk == 0) {
+        const int seat = seats[r];
+        folds[((size_t)r * (2 * max_blocks + 1) + 2 * max_blocks) * W + c] =
+            (seat >= 0 && seat < n_seats) ? state[(size_t)seat * state_stride + c] : 0.f;
+    }
+    if (begin >= end) return;
+    const float bz = bias[c], bx = bias[W + c];
+    const size_t ld = (size_t)3 * W;
+    float A = 1.f, B = 0.f;
+    for (int t0 = begin; t0 < end; t0 += GRU_AHEAD) {
+        float zl[GRU_AHEAD], xl[GRU_AHEAD];
+#pragma unroll
+        for (int i = 0; i < GRU_AHEAD; ++i) {
+            const int t = min(t0 + i, end - 1);
+            zl[i] = zxg[t * ld + c]; xl[i] = zxg[t * ld + W + c];
+        }
+#pragma unroll
+        for (int i = 0; i < GRU_AHEAD; ++i) {
+            if (t0 + i < end) {
+                const GruStep s = gru_step(zl[i], xl[i], bz, bx);
+                A *= s.a;
+                B = fmaf(s.a, B, s.b);
+            }
+        }
+    }
+    float* f = folds + ((size_t)r * (2 * max_blocks + 1) + 2 * blk) * W;
+    f[c] = A;
+    f[W + c] = B;
+}
+
+template <typename T>
+__global__ void mingru_blocks_kernel(const float* __restrict__ zxg, const float* __restrict__ bias, float* state, long long state_stride,
+                                     const int* __restrict__ seats, const int* __restrict__ cu_q, const float* __restrict__ folds,
+                                     T* __restrict__ out, int W, int span, int max_blocks, int n_seats) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    const int r = blockIdx.z, blk = blockIdx.y;
+    const int begin = cu_q[r] + blk * span, last = cu_q[r + 1], end = min(last, begin + span);
+    if (begin >= end) return;
+    const int seat = seats[r];
+    float* mine = (seat >= 0 && seat < n_seats) ? state + (size_t)seat * state_stride : nullptr;
+    // the kept state is read from the copy the kernel before made: the request's last block overwrites the original, and it
+    // may be done before another block of the request has begun
+    const float* f = folds + (size_t)r * (2 * max_blocks + 1) * W;
+    float S = f[(size_t)2 * max_blocks * W + c];
+    for (int b = 0; b < blk; ++b) S = fmaf(f[(size_t)b * 2 * W + c], S, f[(size_t)b * 2 * W + W + c]);
+    const float bz = bias[c], bx = bias[W + c];
+    const size_t ld = (size_t)3 * W;
+    for (int t0 = begin; t0 < end; t0 += GRU_AHEAD) {
+        float zl[GRU_AHEAD], xl[GRU_AHEAD], gl[GRU_AHEAD];
+#pragma unroll
+        for (int i = 0; i < GRU_AHEAD; ++i) {
+            const int t = min(t0 + i, end - 1);
+            zl[i] = zxg[t * ld + c]; xl[i] = zxg[t * ld + W + c]; gl[i] = zxg[t * ld + 2 * W + c];
+        }
+#pragma unroll
+        for (int i = 0; i < GRU_AHEAD; ++i) {
+            if (t0 + i < end) {
+                const GruStep s = gru_step(zl[i], xl[i], bz, bx);
+                S = fmaf(s.a, S, s.b);
+                out[(size_t)(t0 + i) * W + c] = from_float<T>(S * silu(gl[i]));
+            }
+        }
+    }
+    if (mine && end == last) mine[c] = S;
+}
+
+// Floats of scratch the blocked form needs: (A, B) per request, block and channel, and a copy of every request's state.
+extern "C" long long fe_mingru_scan_scratch_floats(int requests, int W, int max_q_len, int span) {
+    if (span <= 0 || max_q_len <= span) return 0;
+    return (long long)requests * (2 * ((max_q_len + span - 1) / span) + 1) * W;
+}
+
+// ``span`` > 0 and ``max_q_len`` > span: the blocked form over blocks of ``span`` tokens (``folds``: scratch); else one walk.
+extern "C" int fe_mingru_scan(const float* zxg, const float* bias, float* state, long long state_stride, const int* seats,
+                              const int* cu_q, void* out, int requests, int W, int n_seats, int max_q_len, int span, float* folds,
+                              int dtype, cudaStream_t stream) {
+    FE_REQUIRE(requests >= 0 && W > 0 && n_seats >= 0 && state_stride >= W, "mingru_scan: bad sizes");
+    FE_REQUIRE(dtype == FE_F32 || dtype == FE_BF16, "mingru_scan: unknown dtype %d", dtype);
+    if (requests == 0) return 0;
+    const int threads = 128;
+    const int columns = (W + threads - 1) / threads;
+    FE_REQUIRE(requests <= 65535, "mingru_scan: too many requests");
+    if (span > 0 && max_q_len > span) {
+        FE_REQUIRE(folds != nullptr, "mingru_scan: the blocked form needs scratch memory");
+        const int max_blocks = (max_q_len + span - 1) / span;
+        FE_REQUIRE(max_blocks <= 65535, "mingru_scan: too many blocks of tokens");
+        const dim3 grid(columns, max_blocks, requests);
+        fe::launch(mingru_fold_kernel, grid, threads, 0, stream, zxg, bias, (const float*)state, state_stride, seats, cu_q, folds, W, span,
+                   max_blocks, n_seats);
+        if (fe_check_launch("mingru_scan fold")) return 1;
+        if (dtype == FE_F32)
+            fe::launch(mingru_blocks_kernel<float>, grid, threads, 0, stream, zxg, bias, state, state_stride, seats, cu_q,
+                       (const float*)folds, (float*)out, W, span, max_blocks, n_seats);
+        else
+            fe::launch(mingru_blocks_kernel<bf16>, grid, threads, 0, stream, zxg, bias, state, state_stride, seats, cu_q,
+                       (const float*)folds, (bf16*)out, W, span, max_blocks, n_seats);
+        return fe_check_launch("mingru_scan blocks");
+    }
+    const dim3 grid(columns, requests);
+    if (dtype == FE_F32)
+        fe::launch(mingru_walk_kernel<float>, grid, threads, 0, stream, zxg, bias, state, state_stride, seats, cu_q, (float*)out, W, n_seats);
+    else
+        fe::launch(mingru_walk_kernel<bf16>, grid, threads, 0, stream, zxg, bias, state, state_stride, seats, cu_q, (bf16*)out, W, n_seats);
+    return fe_check_launch("mingru_scan");
+}
+
+// ---------------------------------------------------------------------------------------------
+// out = act(gate) * up with gate_up = [gate | up] per row; act 0: silu, 1: the tanh form of GELU,
+//   gelu(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int I, int act) {
+    griddep_wait();
+    griddep_launch_dependents();
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const long long t = e / I;
+        const int j = (int)(e - t * I);
+        const float g = to_float(gate_up[t * 2 * I + j]), u = to_float(gate_up[t * 2 * I + I + j]);
+        const float a = act == 0 ? silu(g) : 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+        out[e] = from_float<T>(a * u);
+    }
+}
+
+extern "C" int fe_gated_activation(const void* gate_up, void* out, int T, int I, int act, int dtype, cudaStream_t stream) {
+    FE_REQUIRE(T >= 0 && I > 0 && (act == 0 || act == 1), "gated_activation: bad sizes or activation %d", act);
+    const long long total = (long long)T * I;
+    if (total == 0) return 0;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 65535LL * 8 ? want : 65535LL * 8);
+    if (dtype == FE_F32)
+        fe::launch(gated_activation_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, total, I, act);
+    else if (dtype == FE_BF16)
+        fe::launch(gated_activation_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)out, total, I, act);
+    else
+        FE_REQUIRE(false, "gated_activation: unknown dtype %d", dtype);
+    return fe_check_launch("gated_activation");
+}

@@ -100,10 +100,17 @@ def check_status(device) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
-def embedding(token_ids, table):
-    """float32 residual rows [T, H] = table[token_ids]."""
+def embedding(token_ids, table, scale=1.0, streams=None):
+    """float32 residual rows [T, H] = table[token_ids]; with ``scale`` or ``streams``, rows times ``scale`` as
+    [streams, T, H] (every copy the same), or [T, H] for ``streams`` None."""
     _need_cuda(token_ids, table)
     T, (V, H) = token_ids.numel(), table.shape
+    if scale != 1.0 or streams is not None:
+        copies = 1 if streams is None else int(streams)
+        out = torch.empty((copies, T, H), dtype=torch.float32, device=table.device)
+        _run(_core(), "fe_embedding_streams", _ptr(token_ids), _ptr(table), _ptr(out), _c_int(T), _c_int(H), _c_int(V), _c_float(scale),
+             _c_int(copies), _c_int(_code(table.dtype)), _ptr(status_word(table.device)), _stream())
+        return out[0] if streams is None else out
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     _run(_core(), "fe_embedding", _ptr(token_ids), _ptr(table), _ptr(out), _c_int(T), _c_int(H), _c_int(V),
          _c_int(_code(table.dtype)), _ptr(status_word(table.device)), _stream())
@@ -326,6 +333,33 @@ def linear_swiglu(x, w, intermediate, upcoming=None):
     return swiglu(linear(x, w), intermediate)
 
 
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_activation(gate_up, intermediate, activation):
+    """act(gate) * up of rows [gate | up]; act "silu" or "gelu_tanh" (the tanh form of GELU), float arithmetic."""
+    _need_cuda(gate_up)
+    T = gate_up.shape[0]
+    if gate_up.shape[1] != 2 * intermediate or not gate_up.is_contiguous():
+        raise ValueError("gated_activation: input must be contiguous [T, 2 * intermediate]")
+    if activation not in GATE_ACTIVATIONS:
+        raise ValueError(f"unknown gate activation {activation!r}; known: {sorted(GATE_ACTIVATIONS)}")
+    out = torch.empty((T, intermediate), dtype=gate_up.dtype, device=gate_up.device)
+    _run(_core(), "fe_gated_activation", _ptr(gate_up), _ptr(out), _c_int(T), _c_int(intermediate),
+         _c_int(GATE_ACTIVATIONS[activation]), _c_int(_code(gate_up.dtype)), _stream())
+    return out
+
+
+def linear_gated(x, w, intermediate, activation):
+    """act(x Wg^T) * (x Wu^T) with w = [Wg; Wu] ([2I, K]).  "silu" takes the fused kernels of ``linear_swiglu``; another
+    gate function the product and the activation kernel."""
+    if activation == "silu":
+        return linear_swiglu(x, w, intermediate)
+    if isinstance(x, Prenormed):
+        x = x.materialize()
+    return gated_activation(linear(x, w), intermediate, activation)
+
+
 def qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache,
                         nq, nkv, d, page_size, src=None):
     """qkv [T, (nq + 2 nkv) d] = projection + bias, with the rotary encoding of the query and key heads;
@@ -392,12 +426,12 @@ def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, 
 
 
 def paged_attention_simt(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, token_request, T, nq, nkv, d,
-                         page_size, scale, window):
+                         page_size, scale, window, sink=False):
     out = torch.empty((T, nq * d), dtype=k_cache.dtype, device=k_cache.device)
     _run(_core(), "fe_paged_attention_simt", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start),
          _ptr(token_request), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size),
-         _c_int(k_cache.shape[0]), _c_float(scale), _c_int(window), _c_int(_code(k_cache.dtype)),
+         _c_int(k_cache.shape[0]), _c_float(scale), _c_int(window), _c_int(1 if sink else 0), _c_int(_code(k_cache.dtype)),
          _ptr(status_word(k_cache.device)), _stream())
     return out
 
@@ -458,7 +492,7 @@ def decode_splits(requests: int, nkv: int, max_ctx_len: int, sms: int | None = N
 
 
 def paged_decode_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, requests, nq, nkv, d, page_size,
-                     scale, window, splits, out=None, upcoming=None):
+                     scale, window, splits, out=None, upcoming=None, sink=False):
     """Tensor-core decode attention (one token per request), keys split ``splits`` ways.  ``upcoming``: the
     matrix that the next kernel streams (the output projection); extra blocks of the merge kernel ask for its
     start to be brought into L2."""
@@ -470,7 +504,8 @@ def paged_decode_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, 
     _run(lib, "fe_paged_decode_mma_upcoming", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(out.stride(0)), _ptr(work),
          _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start),
          _c_int(requests), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
-         _c_float(scale), _c_int(window), _c_int(splits), *_upcoming(upcoming, requests, UPCOMING_BYTES_MERGE),
+         _c_float(scale), _c_int(window), _c_int(1 if sink else 0), _c_int(splits),
+         *_upcoming(upcoming, requests, UPCOMING_BYTES_MERGE),
          _ptr(status_word(k_cache.device)), _stream())
     return out
 
@@ -516,7 +551,7 @@ def decode_cluster_splits(splits: int, max_ctx_len: int, clusters: int = 0, resi
 
 
 def paged_decode_cluster(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, requests, nq, nkv, d, page_size,
-                         scale, window, splits, out=None):
+                         scale, window, splits, out=None, sink=False):
     """Decode attention with the splits of each (request, key/value head) as one thread-block cluster that merges
     its partial results through distributed shared memory: one launch, no scratch memory; splits <= 16."""
     if out is None:
@@ -524,18 +559,18 @@ def paged_decode_cluster(q, q_stride, k_cache, v_cache, block_table, cu_q, q_sta
     _run(_bf16(), "fe_paged_decode_cluster", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(out.stride(0)), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
          _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]), _c_float(scale), _c_int(window),
-         _c_int(splits), _ptr(status_word(k_cache.device)), _stream())
+         _c_int(1 if sink else 0), _c_int(splits), _ptr(status_word(k_cache.device)), _stream())
     return out
 
 
 def paged_prefill_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, T, requests, max_q_len, nq, nkv, d,
-                      page_size, scale, window):
+                      page_size, scale, window, sink=False):
     """Tensor-core attention for portions of any length (decoded tokens are portions of one)."""
     out = torch.empty((T, nq * d), dtype=torch.bfloat16, device=k_cache.device)
     _run(_bf16(), "fe_paged_prefill_mma", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
          _c_int(max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
-         _c_float(scale), _c_int(window), _ptr(status_word(k_cache.device)), _stream())
+         _c_float(scale), _c_int(window), _c_int(1 if sink else 0), _ptr(status_word(k_cache.device)), _stream())
     return out
 
 
@@ -568,7 +603,10 @@ def prefill_splits(lengths, starts, nq, nkv, window=0, sms: int | None = None) -
     context, so its keys are split until the blocks about cover the device."""
     group = nq // nkv
     blocks = nkv * sum(-(-n * group // 256) for n in lengths)
-    longest = max(min(s + n, window + n) if window > 0 else s + n for s, n in zip(starts, lengths))
+    if window < 0:      # chunks of -window positions: a portion's rows see their own chunk, and the chunk's start may be far from theirs
+        longest = max(min(s + n, -window + n) for s, n in zip(starts, lengths))
+    else:
+        longest = max(min(s + n, window + n) if window > 0 else s + n for s, n in zip(starts, lengths))
     tiles = -(-longest // 64)
     if tiles < PREFILL_SPLIT_FROM_TILES:
         return 1
@@ -576,7 +614,7 @@ def prefill_splits(lengths, starts, nq, nkv, window=0, sms: int | None = None) -
 
 
 def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, T, requests, max_q_len, nq, nkv, d,
-                          page_size, scale, window, splits=1):
+                          page_size, scale, window, splits=1, sink=False):
     """Prefill attention on tcgen05 tensor cores: 128 (query, head) rows a block, head sizes 64 and 128.
     ``splits`` > 1 shares the keys of each pair of row tiles out over that many blocks and merges their results."""
     out = torch.empty((T, nq * d), dtype=torch.bfloat16, device=k_cache.device)
@@ -584,14 +622,16 @@ def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_st
     _run(_bf16(), "fe_paged_prefill_tcgen05", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
          _c_int(max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
-         _c_float(scale), _c_int(window), _c_int(splits), _ptr(part),
+         _c_float(scale), _c_int(window), _c_int(1 if sink else 0), _c_int(splits), _ptr(part),
          _c_ll(T), _ptr(status_word(k_cache.device)), _stream())
     return out
 
 
-def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window, upcoming=None):
+def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window, upcoming=None, sink=False):
     """Causal grouped-query attention of the step's tokens over their requests' pages.
     qkv [T, >= nq d] holds the (rotated) queries in its first nq d columns; returns [T, nq d].
+    ``window``: what a query sees of the earlier keys: 0 all of them, w > 0 the last w, -c < 0 those of its own chunk of
+    c positions (counted from position 0).  ``sink``: 1 is added to the softmax's denominator.
     float32 runs on CUDA cores (true 32-bit); bfloat16 on tensor cores: the split-KV decode
     kernel when every request brings one token, else a prefill kernel (tcgen05 for portions of
     head size 64 or 128, mma.sync otherwise)."""
@@ -601,7 +641,7 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
         raise TypeError("queries and cache differ in dtype")
     if qkv.dtype == torch.float32 or d > 256:          # the tensor-core kernels take head sizes up to 256
         return paged_attention_simt(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start,
-                                    ctx.token_request, T, nq, nkv, d, page_size, scale, window)
+                                    ctx.token_request, T, nq, nkv, d, page_size, scale, window, sink)
     requests = ctx.cu_q.numel() - 1
     if ctx.max_q_len == 1 and nq // nkv <= 16:
         splits = decode_splits(requests, nkv, ctx.max_ctx_len)
@@ -609,16 +649,139 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
                                           lambda s: clusters_resident(requests, nq, nkv, d, s))
         if clustered:
             return paged_decode_cluster(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
-                                        nq, nkv, d, page_size, scale, window, clustered)
+                                        nq, nkv, d, page_size, scale, window, clustered, sink=sink)
         return paged_decode_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
-                                nq, nkv, d, page_size, scale, window, splits, upcoming=upcoming)
+                                nq, nkv, d, page_size, scale, window, splits, upcoming=upcoming, sink=sink)
     lengths = getattr(ctx, "host_lengths", None)
     if tcgen05_attention_ok(ctx.max_q_len, nq, nkv, d, lengths, getattr(ctx, "host_starts", None)):
         splits = prefill_splits(lengths, ctx.host_starts, nq, nkv, window) if lengths else 1
         return paged_prefill_tcgen05(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
-                                     ctx.max_q_len, nq, nkv, d, page_size, scale, window, splits)
+                                     ctx.max_q_len, nq, nkv, d, page_size, scale, window, splits, sink=sink)
     return paged_prefill_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
-                             ctx.max_q_len, nq, nkv, d, page_size, scale, window)
+                             ctx.max_q_len, nq, nkv, d, page_size, scale, window, sink=sink)
+
+
+# ---- several residual streams, token shift, gated attention, minGRU ---------------------------------------------
+def stream_rmsnorm(streams, read, weight, eps, out_dtype, update=None, rows=None):
+    """RMSNorm of u = sum_s read[s] x_s over the residual streams x [S, T, H] (float32; ``read`` None: the plain sum).
+    ``update`` (an object with y, gate [T, H] in the compute dtype, gate_bias [H], mix [S, S], write [S]) is put into the
+    streams first, in the same kernel: x_t <- sum_s mix[s, t] x_s + write[t] * y * sigmoid(gate + gate_bias), every stream
+    from the old ones.  rows=None: all rows, the streams updated in place; rows given: only those rows are read and
+    nothing is written back."""
+    _need_cuda(streams, read, weight, rows)
+    if streams.dim() != 3 or streams.dtype != torch.float32 or not streams.is_contiguous() or weight.dtype != torch.float32:
+        raise TypeError("stream_rmsnorm: the residual streams are contiguous float32 [S, T, H], norm weights float32")
+    S, T, H = streams.shape
+    if read is not None and (read.dtype != torch.float32 or read.numel() != S):
+        raise ValueError("stream_rmsnorm: read is float32 [S]")
+    y = gate = gate_bias = mix = write = None
+    if update is not None:
+        y, gate, gate_bias, mix, write = update.y, update.gate, update.gate_bias, update.mix, update.write
+        _need_cuda(y, gate, gate_bias, mix, write)
+        if y.dtype != out_dtype or gate.dtype != out_dtype or tuple(y.shape) != (T, H) or tuple(gate.shape) != (T, H) \
+                or not (y.is_contiguous() and gate.is_contiguous()) or gate_bias.dtype != torch.float32 or gate_bias.numel() != H \
+                or mix.dtype != torch.float32 or tuple(mix.shape) != (S, S) or write.dtype != torch.float32 or write.numel() != S \
+                or not mix.is_contiguous():
+            raise ValueError("stream_rmsnorm: the update's rows are contiguous [T, H] in the compute dtype; bias [H], mix [S, S] and "
+                             "write [S] float32")
+    n_out = T if rows is None else rows.numel()
+    out = torch.empty((n_out, H), dtype=out_dtype, device=streams.device)
+    _run(_core(), "fe_stream_rmsnorm", _ptr(streams), _c_int(S), _c_int(T), _c_int(H), _ptr(read), _ptr(weight), _c_float(eps), _ptr(y),
+         _ptr(gate), _ptr(gate_bias), _ptr(mix), _ptr(write), _ptr(rows), _c_int(n_out), _ptr(out), _c_int(_code(out_dtype)), _stream())
+    return out
+
+
+def token_shift(h, mu, kept, state_slots, cu_q, token_request):
+    """h + (h' - h) * mu, h' the row of the token before; a portion's first token takes the row its seat kept (``kept``
+    [seats, H] float32, zeros for a seat below 0), which then becomes this step's last row."""
+    _need_cuda(h, mu, kept, state_slots, cu_q, token_request)
+    T, H = h.shape
+    if mu.dtype != torch.float32 or mu.numel() != H or kept.dtype != torch.float32 or kept.stride(-1) != 1 or kept.shape[-1] < H \
+            or not h.is_contiguous():
+        raise ValueError("token_shift: mu is float32 [H]; the kept rows are float32 with unit stride")
+    out = torch.empty_like(h)
+    _run(_core(), "fe_token_shift", _ptr(h), _ptr(mu), _ptr(kept), _c_ll(kept.stride(0)), _ptr(state_slots), _ptr(cu_q),
+         _ptr(token_request), _ptr(out), _c_int(T), _c_int(H), _c_int(kept.shape[0]), _c_int(_code(h.dtype)), _stream())
+    return out
+
+
+def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, token_request, positions, inv_freq, rot_dims,
+                             qk_norm, eps, slot_mapping, k_cache, v_cache, heads, kv_heads, dim, vdim, head, page_size):
+    """What attention does between its projection and its scores, in one kernel (csrc/hyper_ops.cu).  ``projected``
+    [T, >= channels] holds q | k | v (``heads`` and ``kv_heads`` heads of ``dim``, ``kv_heads`` of ``vdim``).  A causal
+    convolution of ``taps`` taps over time per channel (``conv`` [channels, taps] float32, None for none; ``history``
+    [seats, (taps - 1) channels] float32 holds every request's last taps - 1 projected rows and is brought up to date), the
+    first ``rot_dims`` entries of every query and key head turned by position * inv_freq (pairs i, i + rot_dims/2), queries
+    and keys divided by their root mean square (``qk_norm``), keys and values into their cache slots
+    [pages, kv_heads, page_size, head] (slot_mapping None: no write) and the queries returned [T, heads head], all padded
+    with zeros from dim or vdim to ``head``."""
+    _need_cuda(projected, conv, history, state_slots, cu_q, token_request, positions, inv_freq, slot_mapping, k_cache, v_cache)
+    T = projected.shape[0]
+    channels = (heads + kv_heads) * dim + kv_heads * vdim
+    if projected.dim() != 2 or projected.shape[1] < channels or projected.stride(1) != 1:
+        raise ValueError("qkv_conv_rope_norm_cache: projected is [T, >= channels] with unit column stride")
+    if k_cache.dtype != projected.dtype or tuple(k_cache.shape[1:]) != (kv_heads, page_size, head) or not k_cache.is_contiguous() \
+            or not v_cache.is_contiguous() or v_cache.shape != k_cache.shape:
+        raise ValueError("qkv_conv_rope_norm_cache: caches are contiguous [pages, kv_heads, page_size, head] in the compute dtype")
+    if conv is not None and (conv.dtype != torch.float32 or tuple(conv.shape) != (channels, taps) or not conv.is_contiguous()):
+        raise ValueError("qkv_conv_rope_norm_cache: conv is contiguous float32 [channels, taps]")
+    if conv is None:
+        taps = 0
+    if taps > 1 and (history is None or history.dtype != torch.float32 or history.stride(-1) != 1
+                     or history.shape[-1] < (taps - 1) * channels):
+        raise ValueError("qkv_conv_rope_norm_cache: history is float32 [seats, (taps - 1) channels]")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2):
+        raise ValueError("inv_freq must be float32 [rot_dims / 2]")
+    queries = torch.empty((T, heads * head), dtype=projected.dtype, device=projected.device)
+    seats = history.shape[0] if history is not None else 0
+    _run(_core(), "fe_qkv_conv_rope_norm_cache", _ptr(projected), _c_ll(projected.stride(0)), _ptr(conv), _ptr(history if taps > 1 else None),
+         _c_ll(history.stride(0) if history is not None else 0), _c_int(taps), _ptr(state_slots), _ptr(cu_q), _ptr(token_request),
+         _ptr(positions), _ptr(inv_freq), _c_int(rot_dims if inv_freq is not None else 0), _c_int(1 if qk_norm else 0), _c_float(eps),
+         _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _ptr(queries), _c_int(T), _c_int(heads), _c_int(kv_heads), _c_int(dim),
+         _c_int(vdim), _c_int(head), _c_int(page_size), _c_ll(k_cache.shape[0] * page_size), _c_int(seats),
+         _c_int(_code(projected.dtype)), _ptr(status_word(projected.device)), _stream())
+    return queries
+
+
+def head_gate(mixed, projected, offset, heads, head, vdim):
+    """[T, heads vdim]: out[t, h, :vdim] = mixed[t, h, :vdim] * sigmoid(projected[t, offset + h]); ``mixed`` [T, heads head]."""
+    _need_cuda(mixed, projected)
+    T = mixed.shape[0]
+    if tuple(mixed.shape) != (T, heads * head) or not mixed.is_contiguous() or projected.dtype != mixed.dtype \
+            or projected.stride(1) != 1 or projected.shape[1] < offset + heads:
+        raise ValueError("head_gate: shapes or dtypes do not fit")
+    out = torch.empty((T, heads * vdim), dtype=mixed.dtype, device=mixed.device)
+    gates = projected[:, offset:]
+    _run(_core(), "fe_head_gate", _ptr(mixed), _ptr(gates), _c_ll(projected.stride(0)), _ptr(out), _c_int(T), _c_int(heads),
+         _c_int(head), _c_int(vdim), _c_int(_code(mixed.dtype)), _stream())
+    return out
+
+
+MINGRU_SPAN = 64              # tokens a block of the blocked recurrence walks
+MINGRU_BLOCKED_FROM = 256     # portions at least this long are scanned in blocks
+
+
+def mingru_scan(zxg, bias, state, state_slots, cu_q, width, out_dtype, max_q_len=0):
+    """The minGRU recurrence over the step's tokens (csrc/hyper_ops.cu): zxg [T, 3 width] float32 holds the projections of
+    the gate, the candidate and the output gate; z = sigmoid(. + bias[:W]), u = . + bias[W:], c = u + 1/2 where u >= 0 else
+    sigmoid(u), S <- (1 - z) S + z c from state[seat] (float32 [seats, W]; zeros and nothing kept for a seat below 0),
+    out = S * silu(g) in ``out_dtype``.  ``max_q_len``: the longest portion of the step; long ones are scanned in blocks."""
+    _need_cuda(zxg, bias, state, state_slots, cu_q)
+    T, W = zxg.shape[0], int(width)
+    if zxg.dtype != torch.float32 or tuple(zxg.shape) != (T, 3 * W) or not zxg.is_contiguous() or bias.dtype != torch.float32 \
+            or bias.numel() != 2 * W or state.dtype != torch.float32 or state.stride(-1) != 1 or state.shape[-1] < W:
+        raise ValueError("mingru_scan: zxg is contiguous float32 [T, 3 W], bias float32 [2 W], the state float32 [seats, W]")
+    requests = cu_q.numel() - 1
+    out = torch.empty((T, W), dtype=out_dtype, device=zxg.device)
+    span, folds = 0, None
+    if max_q_len >= MINGRU_BLOCKED_FROM:
+        span = MINGRU_SPAN
+        need = _core().fe_mingru_scan_scratch_floats(_c_int(requests), _c_int(W), _c_int(max_q_len), _c_int(span))
+        folds = torch.empty(max(int(need), 1), dtype=torch.float32, device=zxg.device)
+    _run(_core(), "fe_mingru_scan", _ptr(zxg), _ptr(bias), _ptr(state), _c_ll(state.stride(0)), _ptr(state_slots), _ptr(cu_q), _ptr(out),
+         _c_int(requests), _c_int(W), _c_int(state.shape[0]), _c_int(max_q_len), _c_int(span), _ptr(folds), _c_int(_code(out_dtype)),
+         _stream())
+    return out
 
 
 # ---- the stream: hashed pair embedding, grouped norm, average over depth, activations ---------------------------
