@@ -1,4 +1,4 @@
-"""``--workload fuvozen``: prefill and decode throughput of the Fuvozen design at a few sizes that resemble a real
+"""``--workload fuvozen|fuvuvik``: prefill and decode throughput of one of these designs at a few sizes that resemble a real
 model's layers (random weights), beside a Qwen2 decoder of equal width, depth and vocabulary, and, at one size, an
 operation-by-operation table of both: time, the bytes and flops of the work, and how far each operation is from the
 roofline of the measured peaks (time / max(bytes / copy rate, flops / bf16 rate)).
@@ -32,6 +32,30 @@ def fuvozen_config(width, layers, vocab, heads, experts=8, top=2):
                                   "shared": {"ff": width}}})
     return {"architecture": "Fuvozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 2},
             "embedding": {"bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 7}}, "layers": stack}
+
+
+def fuvuvik_config(width, layers, vocab, heads):
+    """Layers in turns of four: attention with convolutions of four taps, two minGRU recurrences of 1.5 x width, attention in
+    chunks of 1,024 with a sink; heads of 128 in groups of four, half of a head rotated in the first kind; two residual
+    streams; a gated feed-forward of 2 x width, which with the two residual gates of a layer holds the 8 width^2 of the
+    Qwen2 decoder's feed-forward beside it."""
+    stack = []
+    for i in range(layers):
+        turn = i % 4
+        if turn == 0:
+            mixer = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "conv": 4,
+                                                    "rot": {"base": 10000.0, "dims": 64}, "scale": 128 ** -0.5}}
+        elif turn == 3:
+            mixer = {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                                                      "mask": {"size": 1024}, "rot": {"base": 500000.0, "dims": 128}, "scale": 128 ** -0.5}}
+        else:
+            mixer = {"type": "mingru", "mixer": {"width": width * 3 // 2}}
+        stack.append(dict(mixer, mlp={"kind": "dense", "ff": 2 * width}))
+    return {"architecture": "Fuvuvik", "vocab": vocab, "width": width, "streams": 2, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": stack}
+
+
+DESIGNS = {"fuvozen": ("Fuvozen", fuvozen_config), "fuvuvik": ("Fuvuvik", fuvuvik_config)}
 
 
 def qwen2_config(width, layers, vocab, heads):
@@ -77,7 +101,7 @@ class TimedOps:
                     seen.add(t.data_ptr())
                     nbytes += t.numel() * t.element_size()
             flops = 0.0
-            if name in ("linear", "linear_swiglu") and len(args) >= 2:
+            if name in ("linear", "linear_swiglu", "linear_gated") and len(args) >= 2:
                 flops = 2.0 * args[0].shape[0] * args[1].shape[0] * args[1].shape[1]
             elif name == "batched_linear":
                 flops = 2.0 * args[0].shape[0] * args[0].shape[1] * args[0].shape[2] * args[1].shape[1]
@@ -88,19 +112,32 @@ class TimedOps:
                 nbytes = nbytes - (args[3].numel() + args[4].numel()) * 2 * (1 - used / args[3].shape[0])
             elif name in ("paged_attention",):
                 ctx, nq, d = args[4], args[5], args[7]
-                window = args[10]
+                window = args[10]                 # w > 0: the last w keys; -c < 0: the keys of the query's chunk of c positions
+                sees = lambda p: (min(p + 1, window) if window > 0 else (p % -window + 1 if window < 0 else p + 1))
                 pairs = 0
                 for s, n in zip(ctx.host_starts, ctx.host_lengths):
-                    for p in (s, s + n - 1):
-                        pairs += (min(p + 1, window) if window else p + 1) * n / 2.0
+                    if window < 0:
+                        pairs += sum(sees(p) for p in range(s, s + n))
+                    else:
+                        pairs += (sees(s) + sees(s + n - 1)) * n / 2.0
                 flops = 4.0 * nq * d * pairs
                 page, kv = args[8], args[6]
-                keys = sum(min(s + n, (window + n) if window else s + n) for s, n in zip(ctx.host_starts, ctx.host_lengths))
+                reach = abs(window)
+                keys = sum(min(s + n, (reach + n) if reach else s + n) for s, n in zip(ctx.host_starts, ctx.host_lengths))
                 nbytes = args[0].numel() * 2 + 2 * args[0].shape[0] * nq * d + keys * kv * d * 2 * (1 if args[1].data_ptr() == args[2].data_ptr() else 2)
             elif name == "wkv_recurrence":
                 flops = 6.0 * args[0].shape[0] * args[9] * args[10] * args[10]
                 nbytes = args[0].numel() * (3 * args[0].element_size() + 8) + 2 * 4 * (args[8].numel() - 1) * args[9] * args[10] * args[10]
-            shapes = "x".join(str(tuple(a.shape)) for a in args[:2] if torch.is_tensor(a)) if name in ("linear", "linear_swiglu", "batched_linear") else ""
+            elif name == "stream_rmsnorm":
+                # the streams are read, and written back when a sublayer's output goes in; its output and gate are read
+                update = kwargs.get("update")
+                streams = args[0].numel() * 4
+                nbytes = streams * (2 if update is not None and kwargs.get("rows") is None else 1) + (out.numel() * out.element_size())
+                if update is not None:
+                    nbytes += update.y.numel() * update.y.element_size() * 2
+                if kwargs.get("rows") is not None:
+                    nbytes = nbytes * kwargs["rows"].numel() / max(1, args[0].shape[1])
+            shapes = "x".join(str(tuple(a.shape)) for a in args[:2] if torch.is_tensor(a)) if name in ("linear", "linear_swiglu", "linear_gated", "batched_linear") else ""
             row = self.rows.setdefault(f"{name} {shapes}".strip(), [0, 0.0, 0.0, 0.0])
             row[0] += 1
             row[1] += start.elapsed_time(end) * 1e3
@@ -133,6 +170,8 @@ def run(args) -> int:
     gen = torch.Generator().manual_seed(1)
     results, tables = {}, {}
     sizes = [args.size] if getattr(args, "size", None) else list(SIZES)
+    design, design_config = DESIGNS[args.workload]
+    key = args.workload
 
     def measure(cfg, vocab, provider=None, steps=args.steps, warmup=max(args.warmup, 3)):
         _typed, plan, model = random_model(cfg, seed=0, dtype="bfloat16", device=dev)
@@ -180,20 +219,21 @@ def run(args) -> int:
     launches = 0
     for name in sizes:
         width, layers, vocab, heads = SIZES[name]
-        results[name] = {"fuvozen": measure(fuvozen_config(width, layers, vocab, heads), vocab),
+        results[name] = {key: measure(design_config(width, layers, vocab, heads), vocab),
                          "qwen2": measure(qwen2_config(width, layers, vocab, heads), vocab)}
-        launches += results[name]["fuvozen"].pop("launches") + results[name]["qwen2"].pop("launches")
+        launches += results[name][key].pop("launches") + results[name]["qwen2"].pop("launches")
     if args.kernels:
         width, layers, vocab, heads = SIZES[sizes[-1] if getattr(args, "size", None) else "2k"]
-        tables["fuvozen"] = measure(fuvozen_config(width, 2, vocab, heads), vocab, TimedOps(ops, torch))
+        # as many layers as show every kind of layer the design has
+        tables[key] = measure(design_config(width, 2 if key == "fuvozen" else 4, vocab, heads), vocab, TimedOps(ops, torch))
         tables["qwen2"] = measure(qwen2_config(width, 2, vocab, heads), vocab, TimedOps(ops, torch))
     sampler.stop()
-    first = results[sizes[0]]["fuvozen"]
-    line = {"metric": f"decode tokens/s (Fuvozen design, size {sizes[0]}, batch {BATCH}, {PROMPT}-token prompts)",
+    first = results[sizes[0]][key]
+    line = {"metric": f"decode tokens/s ({design} design, size {sizes[0]}, batch {BATCH}, {PROMPT}-token prompts)",
             "value": first["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic: random token ids, random weights", "impl": "ours",
-            "config": {"model": "Fuvozen beside Qwen2 at equal width, depth and vocabulary", "sizes": {k: list(v) for k, v in SIZES.items() if k in sizes},
+            "config": {"model": f"{design} beside Qwen2 at equal width, depth and vocabulary", "sizes": {k: list(v) for k, v in SIZES.items() if k in sizes},
                        "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT, "kv_page": PAGE, "parallelism": "single GPU",
                        "peaks": peak_source},
             "sizes": results, "gpu_launches": launches, "clocks": sampler.summary(timer.windows)}

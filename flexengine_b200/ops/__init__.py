@@ -644,8 +644,10 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
                                     ctx.token_request, T, nq, nkv, d, page_size, scale, window, sink)
     requests = ctx.cu_q.numel() - 1
     if ctx.max_q_len == 1 and nq // nkv <= 16:
-        splits = decode_splits(requests, nkv, ctx.max_ctx_len)
-        clustered = decode_cluster_splits(splits, ctx.max_ctx_len, requests * nkv,
+        # a window or a chunk bounds the keys a token walks (plus the tile of 32 that its first key lies in)
+        span = ctx.max_ctx_len if window == 0 else min(ctx.max_ctx_len, abs(window) + 31)
+        splits = decode_splits(requests, nkv, span)
+        clustered = decode_cluster_splits(splits, span, requests * nkv,
                                           lambda s: clusters_resident(requests, nq, nkv, d, s))
         if clustered:
             return paged_decode_cluster(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,

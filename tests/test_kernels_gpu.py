@@ -266,7 +266,7 @@ def test_a_token_gets_the_same_keys_whichever_projection_path_its_step_takes(nq,
 
 
 def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered", boost=None, splits=None,
-                    simt=False, tcgen05=False, ramp=None, cluster=False):
+                    simt=False, tcgen05=False, ramp=None, cluster=False, sink=False):
     """chunks: [(start, n)] per request.  Fills the cache for positions < start + n."""
     R = len(chunks)
     lens = [s + n for s, n in chunks]
@@ -318,21 +318,21 @@ def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered
         token_request=torch.tensor([r for r, (_, n) in enumerate(chunks) for _ in range(n)], dtype=torch.int32, device=DEV))
     bt = bt.to(DEV)
     scale = 1.0 / math.sqrt(d)
-    want = kernel_refs.paged_attention(qkv, kc, vc, bt, ctx, nq, nkv, d, ps, scale, window)
+    want = kernel_refs.paged_attention(qkv, kc, vc, bt, ctx, nq, nkv, d, ps, scale, window, sink=sink)
     if splits is not None and cluster:   # the same splits as one thread-block cluster per (request, key/value head)
         got = ops().paged_decode_cluster(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, R, nq, nkv, d, ps, scale,
-                                         window, splits)
+                                         window, splits, sink=sink)
     elif splits is not None:          # the split-KV decode kernel, asked for by name
         got = ops().paged_decode_mma(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, R, nq, nkv, d, ps, scale,
-                                     window, splits)
+                                     window, splits, sink=sink)
     elif tcgen05:                     # the tcgen05 prefill kernel, asked for by name; an integer > 1 splits the keys
         got = ops().paged_prefill_tcgen05(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, T, R, ctx.max_q_len, nq,
-                                          nkv, d, ps, scale, window, splits=int(tcgen05))
+                                          nkv, d, ps, scale, window, splits=int(tcgen05), sink=sink)
     elif simt:
         got = ops().paged_attention_simt(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, ctx.token_request, T,
-                                         nq, nkv, d, ps, scale, window)
+                                         nq, nkv, d, ps, scale, window, sink=sink)
     else:
-        got = ops().paged_attention(qkv, kc, vc, bt, ctx, nq, nkv, d, ps, scale, window)
+        got = ops().paged_attention(qkv, kc, vc, bt, ctx, nq, nkv, d, ps, scale, window, sink=sink)
     return got, want, chunks
 
 
@@ -359,6 +359,37 @@ def test_paged_attention_block_tables(dtype, order, gen):
 def test_paged_attention_window(dtype, window, gen):
     got, want, _ = _attention_case(dtype, 4, 2, 32, 16, [(200, 1), (0, 70), (90, 12)], window, gen)
     torch.testing.assert_close(got.float(), want.float(), **bar(dtype))
+
+
+@pytest.mark.parametrize("sink", [False, True])
+@pytest.mark.parametrize("window", [0, 9, -1, -12, -64, -100, -3000])
+def test_chunks_and_a_sink_in_every_attention_kernel(window, sink, gen):
+    """A negative ``window`` is a chunk: a query sees the earlier keys of its own chunk of that many positions, counted from
+    position 0.  ``sink`` adds 1 to the softmax's denominator.  Every kernel by name: CUDA cores in both dtypes, the two
+    decode forms with their splits (of which only the first counts the sink), the mma.sync prefill kernel (head size 32
+    goes there) and the tcgen05 one with and without split keys."""
+    decode = [(p, 1) for p in (0, 1, 11, 12, 63, 64, 100, 255, 700, 2047)]
+    mixed = [(0, 1), (1000, 3), (0, 300), (2000, 70), (63, 2), (500, 129)]
+    for dtype in DTYPES:
+        got, want, _ = _attention_case(dtype, 4, 2, 32, 16, mixed, window, gen, simt=True, sink=sink)
+        torch.testing.assert_close(got.float(), want.float(), **bar(dtype))
+    for splits in (1, 5, 40):
+        got, want, _ = _attention_case(torch.bfloat16, 8, 2, 64, 16, decode, window, gen, splits=splits, sink=sink)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    for splits in (1, 4, 16):
+        got, want, _ = _attention_case(torch.bfloat16, 6, 3, 48, 16, decode, window, gen, splits=splits, cluster=True, sink=sink)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    got, want, _ = _attention_case(torch.bfloat16, 4, 2, 32, 16, mixed, window, gen, sink=sink)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    for splits in (1, 3):
+        for nq, nkv, d, ps in [(8, 2, 128, 16), (5, 1, 64, 8)]:
+            got, want, _ = _attention_case(torch.bfloat16, nq, nkv, d, ps, mixed, window, gen, tcgen05=splits, sink=sink)
+            torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    # scores far below zero: the sink takes almost all of the weight and the output goes to zero
+    if sink:
+        got, want, _ = _attention_case(torch.bfloat16, 4, 2, 64, 16, [(900, 100), (37, 200)], window, gen, tcgen05=2, ramp=-0.6, sink=True)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    ops().check_status(DEV)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
