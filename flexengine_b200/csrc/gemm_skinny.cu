@@ -33,7 +33,12 @@ namespace {
 constexpr int WARPS_USUAL = 8, WARPS_NARROW = 16;
 constexpr int KSTEP = 64;       // k elements per warp step (4 MMAs)
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_RESID = 4 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_RESID = 4, EPI_GEGLU = 5 };   // 5: gated, the tanh form of GELU
+
+// The gate's function of the gated epilogue: 0 silu, 1 the tanh form of GELU, z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gate_function(float z, int act) {
+    return act == 0 ? z / (1.f + expf(-z)) : 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
 
 // The residual epilogue: out[m][n] is not written; residual[m][n] += product, scaled[m][n] = bfloat16(residual *
 // norm_weight[n]), sumsq[tile][m] = this tile's share of the sum of squares of row m of the new residual.
@@ -116,7 +121,7 @@ template <int NT, int EPI, int RT, int PF, int WARPS>
 // blocks an SM: three of the light variant (80 registers a thread), two of the others with eight warps (128)
 __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 1 : (NT == 1 && RT == 1 && PF == 2) ? 3 : NT == 1 ? 2 : 1)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
-                   int I, const QkvEpilogue qkv, const ResidEpilogue resid, const RowScale scale, const int units) {
+                   int I, const QkvEpilogue qkv, const ResidEpilogue resid, const RowScale scale, const int units, const int gate_act) {
     __shared__ float red[WARPS][RT * NT * 8 * 16];
     __shared__ float scale_part[WARPS * 4][8];     // partial sums of squares: [share of the tiles][row]
     extern __shared__ __align__(16) float scale_table[];      // [scale.tiles][8], when the input rows are to be scaled
@@ -337,7 +342,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
                 up += red[w][(r * NT * 8 + m) * 16 + row + 8];
             }
             if (scale.sumsq != nullptr) { gate *= row_scale[m]; up *= row_scale[m]; }
-            reinterpret_cast<bf16*>(out)[(size_t)m * I + n] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+            reinterpret_cast<bf16*>(out)[(size_t)m * I + n] = __float2bfloat16_rn(gate_function(gate, gate_act) * up);
         }
     } else if (EPI == EPI_RESID) {
         // NT == 1: idx = (tile r, row m of the batch, column of the tile); the 16 columns of a (tile, row) sit in
@@ -382,7 +387,8 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
 
 template <int EPI>
 int launch(const void* x, const void* W_, void* out, int M, int N, int K, int I, cudaStream_t stream,
-           const QkvEpilogue& qkv = QkvEpilogue{}, const ResidEpilogue& resid = ResidEpilogue{}, const RowScale& scale = RowScale{}) {
+           const QkvEpilogue& qkv = QkvEpilogue{}, const ResidEpilogue& resid = ResidEpilogue{}, const RowScale& scale = RowScale{},
+           int gate_act = 0) {
     const int tiles = EPI == EPI_SWIGLU ? (I + 7) / 8 : (N + 15) / 16;
     // Three one-tile blocks are resident on an SM (80 registers a thread), two of the others (120 to 128).  A matrix
     // with more tiles than one round of one-tile blocks takes two tiles a block: a few blocks over the round would
@@ -401,7 +407,7 @@ int launch(const void* x, const void* W_, void* out, int M, int N, int K, int I,
     // fewer blocks than SMs, and at least one round of loads (four steps) for each of sixteen warps
     const bool narrow = (EPI == EPI_BF16 || EPI == EPI_F32 || EPI == EPI_RESID) && M <= 8 && tiles <= sms && K / KSTEP >= 4 * WARPS_NARROW;
 #define FE_SKINNY(NT, RT, PF, W) \
-    fe::launch(skinny_gemm_kernel<NT, EPI, RT, PF, W>, blocks, W * 32, table_bytes, stream, (const bf16*)x, (const bf16*)W_, out, M, N, K, I, qkv, resid, scale, units)
+    fe::launch(skinny_gemm_kernel<NT, EPI, RT, PF, W>, blocks, W * 32, table_bytes, stream, (const bf16*)x, (const bf16*)W_, out, M, N, K, I, qkv, resid, scale, units, gate_act)
     if (narrow) FE_SKINNY(1, 1, 4, WARPS_NARROW);
     else if (EPI == EPI_RESID && M > 8) return 1;          // refused by the entry point already
     else if (M <= 8) { if (wide) FE_SKINNY(1, 2, 2, WARPS_USUAL); else if (deep) FE_SKINNY(1, 1, 4, WARPS_USUAL); else FE_SKINNY(1, 1, 2, WARPS_USUAL); }
@@ -424,7 +430,8 @@ static int check_scale(const char* what, const float* sumsq, int sumsq_tiles, in
     return 0;
 }
 
-// epilogue: 0 bfloat16 [M, N]; 1 float [M, N]; 2 SwiGLU: W is [2 I, K] (gate rows, then up rows), out bfloat16 [M, I].
+// epilogue: 0 bfloat16 [M, N]; 1 float [M, N]; 2 SwiGLU: W is [2 I, K] (gate rows, then up rows), out bfloat16 [M, I]; 5 the
+// same with the tanh form of GELU as the gate's function.
 // ``sumsq`` (may be null): see check_scale.
 extern "C" int fe_skinny_gemm_scaled(const void* x, const void* W, void* out, int M, int N, int K, int epilogue,
                                      const float* sumsq, int sumsq_tiles, float eps, const void* next, long long next_bytes,
@@ -437,9 +444,9 @@ extern "C" int fe_skinny_gemm_scaled(const void* x, const void* W, void* out, in
     const RowScale scale{sumsq, sumsq_tiles, eps, K, next, next_bytes};
     if (epilogue == EPI_BF16) return launch<EPI_BF16>(x, W, out, M, N, K, 0, stream, QkvEpilogue{}, ResidEpilogue{}, scale);
     if (epilogue == EPI_F32) return launch<EPI_F32>(x, W, out, M, N, K, 0, stream, QkvEpilogue{}, ResidEpilogue{}, scale);
-    if (epilogue == EPI_SWIGLU) {
-        FE_REQUIRE(N % 2 == 0, "skinny_gemm: SwiGLU needs an even number of weight rows, got %d", N);
-        return launch<EPI_SWIGLU>(x, W, out, M, N, K, N / 2, stream, QkvEpilogue{}, ResidEpilogue{}, scale);
+    if (epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) {
+        FE_REQUIRE(N % 2 == 0, "skinny_gemm: a gated epilogue needs an even number of weight rows, got %d", N);
+        return launch<EPI_SWIGLU>(x, W, out, M, N, K, N / 2, stream, QkvEpilogue{}, ResidEpilogue{}, scale, epilogue == EPI_GEGLU ? 1 : 0);
     }
     FE_REQUIRE(false, "skinny_gemm: unknown epilogue %d", epilogue);
 }

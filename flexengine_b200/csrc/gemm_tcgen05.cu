@@ -38,7 +38,13 @@ constexpr int STAGES = 4;
 constexpr int THREADS = 192;
 constexpr long long WAIT_LIMIT = 4000000000LL;      // clock cycles
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_GEGLU = 5 };      // 5: the gated epilogue with the tanh form of GELU
+
+// The gate's function of the gated epilogue: 0 silu, z / (1 + exp(-z)); 1 the tanh form of GELU,
+// z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gate_function(float z, int act) {
+    return act == 0 ? z / (1.f + expf(-z)) : 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -150,7 +156,7 @@ __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     void* __restrict__ out_raw, int M, int N_out, int K, int up_row_offset, int m_tiles, int n_tiles,
                     const int* __restrict__ g_tiles, const int* __restrict__ g_expert, const int* __restrict__ g_row0,
-                    const int* __restrict__ g_offsets, int w_rows, int* __restrict__ status) {
+                    const int* __restrict__ g_offsets, int w_rows, int gate_act, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
     __shared__ __align__(8) unsigned long long acc_full[ACC_BUFFERS], acc_empty[ACC_BUFFERS];
@@ -257,7 +263,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     float u[32];
                     tmem_load32(lane_addr + 128 + c, u);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = v[j] / (1.f + expf(-v[j])) * u[j];
+                    for (int j = 0; j < 32; ++j) v[j] = gate_function(v[j], gate_act) * u[j];
                 }
                 if (row < row_end && EPI == EPI_F32) {
                     float* dst = reinterpret_cast<float*>(out_raw) + (size_t)row * N_out + n0 + c;
@@ -326,7 +332,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 template <int EPI>
 int launch(const void* x, const void* W, void* out, int M, int N, int K, int* status, cudaStream_t stream,
            const int* g_tiles = nullptr, const int* g_expert = nullptr, const int* g_row0 = nullptr, const int* g_offsets = nullptr,
-           long long w_rows_total = 0) {
+           long long w_rows_total = 0, int gate_act = 0) {
     const int n_out = EPI == EPI_SWIGLU ? N / 2 : N;
     constexpr int OUT_COLS = EPI == EPI_SWIGLU ? 128 : 256;
     CUtensorMap map_a, map_b;
@@ -340,22 +346,23 @@ int launch(const void* x, const void* W, void* out, int M, int N, int K, int* st
     const long long total = (long long)m_tiles * n_tiles;
     const int blocks = g_tiles ? sms : (int)(total < sms ? total : sms);        // one persistent block per SM
     fe::launch(gemm_tcgen05_kernel<EPI>, blocks, THREADS, smem, stream, map_a, map_b, out, M, n_out, K, n_out,
-               m_tiles, n_tiles, g_tiles, g_expert, g_row0, g_offsets, N, status);
+               m_tiles, n_tiles, g_tiles, g_expert, g_row0, g_offsets, N, gate_act, status);
     return fe_check_launch("gemm_tcgen05");
 }
 
 }  // namespace
 
-// epilogue 0: out bfloat16 [M, N]; 2: SwiGLU, W is [N = 2 I, K] (gate rows, then up rows), out bfloat16 [M, I].
+// epilogue 0: out bfloat16 [M, N]; 2: SwiGLU, W is [N = 2 I, K] (gate rows, then up rows), out bfloat16 [M, I]; 5: the same
+// with the tanh form of GELU as the gate's function.
 extern "C" int fe_gemm_tcgen05(const void* x, const void* W, void* out, int M, int N, int K, int epilogue, int* status,
                                cudaStream_t stream) {
     FE_REQUIRE(M >= 1 && N >= 1 && K >= 8, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
     FE_REQUIRE(K % 8 == 0, "gemm_tcgen05: K = %d must be a multiple of 8 (rows must start on 16-byte boundaries)", K);
     FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
     if (epilogue == EPI_BF16) return launch<EPI_BF16>(x, W, out, M, N, K, status, stream);
-    if (epilogue == EPI_SWIGLU) {
-        FE_REQUIRE(N % 2 == 0, "gemm_tcgen05: SwiGLU needs an even number of weight rows, got %d", N);
-        return launch<EPI_SWIGLU>(x, W, out, M, N, K, status, stream);
+    if (epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) {
+        FE_REQUIRE(N % 2 == 0, "gemm_tcgen05: a gated epilogue needs an even number of weight rows, got %d", N);
+        return launch<EPI_SWIGLU>(x, W, out, M, N, K, status, stream, nullptr, nullptr, nullptr, nullptr, 0, epilogue == EPI_GEGLU ? 1 : 0);
     }
     FE_REQUIRE(false, "gemm_tcgen05: unknown epilogue %d", epilogue);
 }

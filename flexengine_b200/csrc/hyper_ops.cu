@@ -114,20 +114,120 @@ __global__ void stream_rmsnorm_kernel(float* __restrict__ x, int S, int T_tokens
     for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_float<T>(u_row[j] * inv * weight[j]);
 }
 
+// The same, four columns a thread at a time (H % 4 == 0): 16-byte loads and stores of the float streams.
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Quad<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                           __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const unsigned*>(&a);
+        raw.y = *reinterpret_cast<const unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename T, int SMAX>
+__global__ void stream_rmsnorm_vec_kernel(float* __restrict__ x, int S, int T_tokens, int H, const float* __restrict__ read,
+                                          const float* __restrict__ weight, float eps, const T* __restrict__ y,
+                                          const T* __restrict__ gate, const float* __restrict__ gate_bias,
+                                          const float* __restrict__ mix, const float* __restrict__ write,
+                                          const int* __restrict__ rows, T* __restrict__ out) {
+    griddep_wait();
+    griddep_launch_dependents();
+    extern __shared__ float u_row[];
+    __shared__ float scratch[33];
+    __shared__ float s_mix[SMAX * SMAX], s_write[SMAX], s_read[SMAX];
+    for (int e = threadIdx.x; e < S * S; e += blockDim.x) s_mix[e] = mix ? mix[e] : 0.f;
+    for (int e = threadIdx.x; e < S; e += blockDim.x) {
+        s_write[e] = write ? write[e] : 0.f;
+        s_read[e] = read ? read[e] : 1.f;
+    }
+    __syncthreads();
+    const int i = blockIdx.x;
+    int r = rows ? rows[i] : i;
+    if (r < 0 || r >= T_tokens) r = 0;              // guarded: rows are checked on the host
+    const size_t plane = (size_t)T_tokens * H;
+    float* base = x + (size_t)r * H;
+    float ss = 0.f;
+    for (int j = threadIdx.x * 4; j < H; j += blockDim.x * 4) {
+        float4 v[SMAX];
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s) v[s] = s < S ? Quad<float>::load(base + s * plane + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (y) {
+            const float4 yy = Quad<T>::load(y + (size_t)r * H + j), gg = Quad<T>::load(gate + (size_t)r * H + j);
+            const float4 bb = Quad<float>::load(gate_bias + j);
+            const float4 g = make_float4(yy.x * sigmoidf(gg.x + bb.x), yy.y * sigmoidf(gg.y + bb.y), yy.z * sigmoidf(gg.z + bb.z),
+                                         yy.w * sigmoidf(gg.w + bb.w));
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t) {
+                if (t < S) {
+                    float4 n = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int s = 0; s < SMAX; ++s) {
+                        if (s < S) {
+                            const float m = s_mix[s * S + t];
+                            n.x = fmaf(m, v[s].x, n.x); n.y = fmaf(m, v[s].y, n.y); n.z = fmaf(m, v[s].z, n.z); n.w = fmaf(m, v[s].w, n.w);
+                        }
+                    }
+                    const float w = s_write[t], rd = s_read[t];
+                    n.x = fmaf(w, g.x, n.x); n.y = fmaf(w, g.y, n.y); n.z = fmaf(w, g.z, n.z); n.w = fmaf(w, g.w, n.w);
+                    if (!rows) Quad<float>::store(base + t * plane + j, n);
+                    u.x = fmaf(rd, n.x, u.x); u.y = fmaf(rd, n.y, u.y); u.z = fmaf(rd, n.z, u.z); u.w = fmaf(rd, n.w, u.w);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < SMAX; ++s) {
+                if (s < S) {
+                    const float rd = s_read[s];
+                    u.x = fmaf(rd, v[s].x, u.x); u.y = fmaf(rd, v[s].y, u.y); u.z = fmaf(rd, v[s].z, u.z); u.w = fmaf(rd, v[s].w, u.w);
+                }
+            }
+        }
+        *reinterpret_cast<float4*>(u_row + j) = u;
+        ss += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)H + eps);
+    T* o = out + (size_t)i * H;
+    for (int j = threadIdx.x * 4; j < H; j += blockDim.x * 4) {
+        const float4 u = *reinterpret_cast<const float4*>(u_row + j), w = Quad<float>::load(weight + j);
+        Quad<T>::store(o + j, make_float4(u.x * inv * w.x, u.y * inv * w.y, u.z * inv * w.z, u.w * inv * w.w));
+    }
+}
+
 template <typename T>
 static int launch_stream_rmsnorm(float* x, int S, int T_tokens, int H, const float* read, const float* weight, float eps, const void* y,
                                  const void* gate, const float* gate_bias, const float* mix, const float* write, const int* rows,
                                  int n_out, void* out, cudaStream_t stream) {
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     const size_t smem = (size_t)H * sizeof(float);
-#define FE_LAUNCH_STREAM_NORM(SMAX)                                                                                       \
-    fe::launch(stream_rmsnorm_kernel<T, SMAX>, n_out, threads, smem, stream, x, S, T_tokens, H, read, weight, eps,       \
+    // four columns a thread when every row, of the streams and of what goes into them, starts on a 16-byte boundary
+    const bool vec = H % 4 == 0 && S <= 8 && (((size_t)x | (size_t)weight | (size_t)gate_bias) & 15) == 0 &&
+                     (((size_t)y | (size_t)gate | (size_t)out) & 15) == 0;
+    const int threads = vec ? (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
+#define FE_LAUNCH_STREAM_NORM(KERNEL, SMAX)                                                                               \
+    fe::launch(KERNEL<T, SMAX>, n_out, threads, smem, stream, x, S, T_tokens, H, read, weight, eps,                      \
                (const T*)y, (const T*)gate, gate_bias, mix, write, rows, (T*)out)
-    if (S <= 1) FE_LAUNCH_STREAM_NORM(1);
-    else if (S <= 2) FE_LAUNCH_STREAM_NORM(2);
-    else if (S <= 4) FE_LAUNCH_STREAM_NORM(4);
-    else if (S <= 8) FE_LAUNCH_STREAM_NORM(8);
-    else FE_LAUNCH_STREAM_NORM(16);
+    if (vec) {
+        if (S <= 1) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_vec_kernel, 1);
+        else if (S <= 2) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_vec_kernel, 2);
+        else if (S <= 4) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_vec_kernel, 4);
+        else FE_LAUNCH_STREAM_NORM(stream_rmsnorm_vec_kernel, 8);
+    } else if (S <= 1) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_kernel, 1);
+    else if (S <= 2) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_kernel, 2);
+    else if (S <= 4) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_kernel, 4);
+    else if (S <= 8) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_kernel, 8);
+    else FE_LAUNCH_STREAM_NORM(stream_rmsnorm_kernel, 16);
 #undef FE_LAUNCH_STREAM_NORM
     return fe_check_launch("stream_rmsnorm");
 }
@@ -357,11 +457,43 @@ __global__ void head_gate_kernel(const T* __restrict__ mixed, const T* __restric
     }
 }
 
+// The same, eight columns of one head a thread (vdim and head multiples of 8): 16- or 32-byte loads and stores.
+template <typename T>
+__global__ void head_gate_vec_kernel(const T* __restrict__ mixed, const T* __restrict__ gates, long long ld, T* __restrict__ out,
+                                     long long groups, int heads, int head, int vdim) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int per_head = vdim >> 3;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < groups; e += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(e % per_head) << 3;
+        const long long th = e / per_head;
+        const int h = (int)(th % heads);
+        const long long t = th / heads;
+        const float g = sigmoidf(to_float(gates[t * ld + h]));
+        float v[8];
+        load8<T>(mixed + (t * heads + h) * head + c, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= g;
+        store8<T>(out + (t * heads + h) * vdim + c, v);
+    }
+}
+
 extern "C" int fe_head_gate(const void* mixed, const void* gates, long long ld, void* out, int T, int heads, int head, int vdim,
                             int dtype, cudaStream_t stream) {
     FE_REQUIRE(T >= 0 && heads > 0 && head >= vdim && vdim > 0, "head_gate: bad sizes");
     const long long total = (long long)T * heads * vdim;
     if (total == 0) return 0;
+    if (vdim % 8 == 0 && head % 8 == 0 && (((size_t)mixed | (size_t)out) & 31) == 0 && (dtype == FE_F32 || dtype == FE_BF16)) {
+        const long long groups = total / 8, want = (groups + 255) / 256;
+        const int blocks = (int)(want < 65535LL * 4 ? want : 65535LL * 4);
+        if (dtype == FE_F32)
+            fe::launch(head_gate_vec_kernel<float>, blocks, 256, 0, stream, (const float*)mixed, (const float*)gates, ld, (float*)out, groups,
+                       heads, head, vdim);
+        else
+            fe::launch(head_gate_vec_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)mixed, (const bf16*)gates, ld, (bf16*)out, groups,
+                       heads, head, vdim);
+        return fe_check_launch("head_gate");
+    }
     const long long want = (total + 255) / 256;
     const int blocks = (int)(want < 65535LL * 4 ? want : 65535LL * 4);
     if (dtype == FE_F32)

@@ -254,7 +254,8 @@ def linear(x, w, bias=None, out_float32=False, follow=None, upcoming=None):
 
 SKINNY_MAX_ROWS = 8          # beyond this the library product is as fast or faster
 SKINNY_QKV_MAX_ROWS = 8      # the fused projection + bias + rotation + cache write takes one 8-row tile of tokens
-EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_GEGLU = 0, 1, 2, 5      # 5: the gated epilogue with the tanh form of GELU
+GATED_EPILOGUES = {"silu": EPI_SWIGLU, "gelu_tanh": EPI_GEGLU}
 
 
 def skinny_ok(x, w) -> bool:
@@ -270,7 +271,7 @@ def skinny_gemm(x, w, epilogue: int = EPI_BF16, upcoming=None):
     x, sumsq, tiles, eps = _rows_and_scale(x)
     M, K = x.shape
     N = w.shape[0]
-    if epilogue == EPI_SWIGLU:
+    if epilogue in (EPI_SWIGLU, EPI_GEGLU):
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
     else:
         out = torch.empty((M, N), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16, device=x.device)
@@ -297,13 +298,13 @@ def tcgen05_ok(x, w) -> bool:
 
 def gemm_tcgen05(x, w, epilogue: int = EPI_BF16):
     """x [M, K] times w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator);
-    epilogue EPI_BF16 or EPI_SWIGLU.  See csrc/gemm_tcgen05.cu."""
+    epilogue EPI_BF16, EPI_SWIGLU or EPI_GEGLU.  See csrc/gemm_tcgen05.cu."""
     _need_cuda(x, w)
     M, K = x.shape
     N = w.shape[0]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_contiguous() or not w.is_contiguous():
         raise TypeError("gemm_tcgen05 takes contiguous bfloat16 operands")
-    out = torch.empty((M, N // 2 if epilogue == EPI_SWIGLU else N), dtype=torch.bfloat16, device=x.device)
+    out = torch.empty((M, N // 2 if epilogue in (EPI_SWIGLU, EPI_GEGLU) else N), dtype=torch.bfloat16, device=x.device)
     _run(_bf16(), "fe_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue),
          _ptr(status_word(x.device)), _stream())
     return out
@@ -351,12 +352,20 @@ def gated_activation(gate_up, intermediate, activation):
 
 
 def linear_gated(x, w, intermediate, activation):
-    """act(x Wg^T) * (x Wu^T) with w = [Wg; Wu] ([2I, K]).  "silu" takes the fused kernels of ``linear_swiglu``; another
-    gate function the product and the activation kernel."""
+    """act(x Wg^T) * (x Wu^T) with w = [Wg; Wu] ([2I, K]), act "silu" or "gelu_tanh": the weight-streaming kernel for a
+    handful of rows and the tcgen05 kernel for a prompt's worth apply the gate's function in their epilogues; otherwise
+    the product and the activation kernel."""
     if activation == "silu":
         return linear_swiglu(x, w, intermediate)
+    if activation not in GATED_EPILOGUES:
+        raise ValueError(f"unknown gate activation {activation!r}; known: {sorted(GATED_EPILOGUES)}")
     if isinstance(x, Prenormed):
         x = x.materialize()
+    if w.shape[0] == 2 * intermediate:
+        if _fits(x, w) == "skinny":
+            return skinny_gemm(x, w, GATED_EPILOGUES[activation])
+        if tcgen05_ok(x, w):
+            return gemm_tcgen05(x, w, GATED_EPILOGUES[activation])
     return gated_activation(linear(x, w), intermediate, activation)
 
 
@@ -759,7 +768,8 @@ def head_gate(mixed, projected, offset, heads, head, vdim):
     return out
 
 
-MINGRU_SPAN = 64              # tokens a block of the blocked recurrence walks
+MINGRU_SPAN = 32              # tokens a block of the blocked recurrence walks; a block then folds up to T / 32 blocks before it,
+MINGRU_SPAN_LONG = 64         # so portions from 4,096 tokens on take blocks of 64
 MINGRU_BLOCKED_FROM = 256     # portions at least this long are scanned in blocks
 
 
@@ -777,7 +787,7 @@ def mingru_scan(zxg, bias, state, state_slots, cu_q, width, out_dtype, max_q_len
     out = torch.empty((T, W), dtype=out_dtype, device=zxg.device)
     span, folds = 0, None
     if max_q_len >= MINGRU_BLOCKED_FROM:
-        span = MINGRU_SPAN
+        span = MINGRU_SPAN if max_q_len < 4096 else MINGRU_SPAN_LONG
         need = _core().fe_mingru_scan_scratch_floats(_c_int(requests), _c_int(W), _c_int(max_q_len), _c_int(span))
         folds = torch.empty(max(int(need), 1), dtype=torch.float32, device=zxg.device)
     _run(_core(), "fe_mingru_scan", _ptr(zxg), _ptr(bias), _ptr(state), _c_ll(state.stride(0)), _ptr(state_slots), _ptr(cu_q), _ptr(out),

@@ -230,13 +230,13 @@ def as64(weights):
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
-@pytest.mark.parametrize("streams", [1, 2, 3, 5])
-def test_stream_norm_and_update_alone(device, dtype, streams):
+@pytest.mark.parametrize("streams,width", [(1, 40), (2, 40), (3, 42), (5, 40), (8, 36), (9, 40), (16, 24)])
+def test_stream_norm_and_update_alone(device, dtype, streams, width):
     """A sublayer's output goes into every stream while they are mixed, then the learned sum is normed: all rows in place,
-    and chosen rows without writing anything."""
+    and chosen rows without writing anything.  Widths that are and are not multiples of four, up to the most streams."""
     dt = getattr(torch, dtype)
     ops = ops_for(device)
-    S, T, D, eps = streams, 9, 40, 1e-5
+    S, T, D, eps = streams, 9, width, 1e-5
     x = torch.randn(S, T, D, generator=torch.Generator().manual_seed(1))
     y, gate = randn(T, D, seed=2), randn(T, D, seed=3)
     bias, mix = randn(D, seed=4), randn(S, S, seed=5)
@@ -284,8 +284,10 @@ def test_gated_feed_forward_alone(device, dtype):
     bind_by_checkpoint_names(part, weights, "", {"gate_up.weight": ["gate", "up"], "down.weight": ["down"]}, device, dt)
     h = randn(T, D, seed=4, scale=2.0)                                       # both tails of the gate function
     ctx = types.SimpleNamespace(ops=ops_for(device), dtype=dt)
-    got = part.forward(ctx, h.to(device=device, dtype=dt))
-    close(got, plain.feed_forward(h.to(F64), as64(weights), ""), dtype, "gated feed-forward", bars=(2e-5, 4e-2))
+    want = plain.feed_forward(h.to(F64), as64(weights), "")
+    for rows in (T, 5):                                                      # a handful of rows takes another kernel in bfloat16
+        got = part.forward(ctx, h[:rows].to(device=device, dtype=dt).contiguous())
+        close(got, want[:rows], dtype, f"gated feed-forward, {rows} rows", bars=(2e-5, 4e-2))
 
 
 def mingru_weights(D, W, seed):
@@ -381,7 +383,8 @@ def run_attention(mixer):
 # heads, kv_heads, dim, vdim, conv, rot_dims: values wider and narrower than keys, no convolution history (one tap), five taps
 # (longer than the shortest portions), no rotation, a whole head rotated, the head size of the fast kernels, one head
 @pytest.mark.parametrize("device,dtype", CASES)
-@pytest.mark.parametrize("shape", [(4, 2, 16, 24, 3, 8), (2, 1, 32, 16, 1, 32), (3, 3, 16, 16, 5, 0), (8, 2, 64, 64, 4, 48), (1, 1, 40, 8, 2, 20)])
+@pytest.mark.parametrize("shape", [(4, 2, 16, 24, 3, 8), (2, 1, 32, 16, 1, 32), (3, 3, 16, 16, 5, 0), (8, 2, 64, 64, 4, 48), (1, 1, 40, 8, 2, 20),
+                                   (2, 1, 16, 12, 2, 8)])
 def test_attention_with_convolutions_alone(device, dtype, shape):
     dt = getattr(torch, dtype)
     D, T = 48, 41

@@ -361,6 +361,22 @@ def test_paged_attention_window(dtype, window, gen):
     torch.testing.assert_close(got.float(), want.float(), **bar(dtype))
 
 
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+@pytest.mark.parametrize("M,I,K", [(1, 256, 128), (4, 200, 256), (8, 1000, 64), (13, 96, 80), (1024, 512, 1024), (1500, 328, 1536)])
+def test_gated_products_whichever_kernel_takes_them(activation, M, I, K, gen):
+    """act(x Wg^T) * (x Wu^T): the weight-streaming kernel (up to 8 rows), the tcgen05 kernel (a prompt's worth of rows) and the
+    library product with the activation kernel, each with both gate functions, against the float product."""
+    x, w = rand((M, K), torch.bfloat16, gen, 2.0), rand((2 * I, K), torch.bfloat16, gen, K ** -0.5)
+    got = ops().linear_gated(x, w, I, activation)
+    want = kernel_refs.gated_activation(kernel_refs.linear(x, w, out_float32=True), I, activation)
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    for dtype in DTYPES:
+        gate_up = rand((7, 2 * I), dtype, gen, 3.0)
+        torch.testing.assert_close(ops().gated_activation(gate_up, I, activation).float(),
+                                   kernel_refs.gated_activation(gate_up, I, activation).float(), **bar(dtype))
+    ops().check_status(DEV)
+
+
 @pytest.mark.parametrize("sink", [False, True])
 @pytest.mark.parametrize("window", [0, 9, -1, -12, -64, -100, -3000])
 def test_chunks_and_a_sink_in_every_attention_kernel(window, sink, gen):
