@@ -146,6 +146,22 @@ class TimedOps:
             return out
         return timed
 
+    def call_floor_us(self, repeats: int = 20) -> float:
+        """What the timing itself costs a call: the device time between the events around a kernel that does next to nothing
+        (an activation of two numbers), taken the same way.  An operation's time in the table includes it."""
+        torch = self._torch
+        tiny = torch.zeros((1, 2), dtype=torch.bfloat16, device="cuda")
+        times = []
+        for _ in range(repeats):
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            self._ops.gated_activation(tiny, 1, "silu")
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end) * 1e3)
+        return round(sorted(times)[len(times) // 2], 1)
+
     def table(self, peaks):
         hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
         out = []
@@ -193,7 +209,7 @@ def run(args) -> int:
             runner.step([StepEntry(rid, [1], [0]) for rid in rids])
             provider.rows.clear()
             runner.step([StepEntry(rid, [2], [0]) for rid in rids])
-            return {"prefill": prefill_table, "decode": provider.table(peaks)}
+            return {"prefill": prefill_table, "decode": provider.table(peaks), "call_floor_us": provider.call_floor_us()}
         for w in range(3):
             prefill_once(-1 - w)
         prefill_ms, _ = timer.timed(prefill_once, 5)

@@ -13,7 +13,9 @@ using namespace fe;
 
 namespace {
 
-__device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + expf(-x)); }
+// 1 / (1 + exp(-x)): the accurate exponential, then the hardware's reciprocal (2 ulp; a full division is half of what a
+// gate costs where a kernel does little else, as the recurrence does)
+__device__ __forceinline__ float sigmoidf(float x) { return __fdividef(1.f, 1.f + expf(-x)); }
 
 constexpr int MAX_STREAMS = 16;
 
@@ -276,10 +278,59 @@ __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restr
     }
 }
 
+// The same, eight columns a thread (D and the kept rows' stride multiples of 8): 16- and 32-byte loads and stores.
+template <typename T>
+__global__ void token_shift_vec_kernel(const T* __restrict__ h, const float* __restrict__ mu, float* kept, long long kept_stride,
+                                       const int* __restrict__ seats, const int* __restrict__ cu_q, const int* __restrict__ token_req,
+                                       T* __restrict__ out, int T_tokens, int D, int n_seats) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int per_row = D >> 3;
+    const long long total = (long long)T_tokens * per_row;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(e / per_row), j = (int)(e - (long long)t * per_row) << 3;
+        const int r = token_req[t];
+        const int first = cu_q[r];
+        float x[8], before[8], m[8];
+        load8<T>(h + (size_t)t * D + j, x);
+        load8<float>(mu + j, m);
+        if (t > first) {
+            load8<T>(h + (size_t)(t - 1) * D + j, before);
+        } else {
+            const int seat = seats[r];
+            if (seat >= 0 && seat < n_seats) {
+                float* mine = kept + (size_t)seat * kept_stride + j;
+                float last[8];
+                load8<float>(mine, before);
+                load8<T>(h + (size_t)(cu_q[r + 1] - 1) * D + j, last);
+                store8<float>(mine, last);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) before[i] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = fmaf(before[i] - x[i], m[i], x[i]);
+        store8<T>(out + (size_t)t * D + j, x);
+    }
+}
+
 extern "C" int fe_token_shift(const void* h, const float* mu, float* kept, long long kept_stride, const int* seats, const int* cu_q,
                               const int* token_req, void* out, int T, int D, int n_seats, int dtype, cudaStream_t stream) {
     FE_REQUIRE(T >= 0 && D > 0 && n_seats >= 0 && kept_stride >= D, "token_shift: bad sizes");
     if (T == 0) return 0;
+    if (D % 8 == 0 && kept_stride % 8 == 0 && (((size_t)h | (size_t)out | (size_t)mu | (size_t)kept) & 31) == 0 &&
+        (dtype == FE_F32 || dtype == FE_BF16)) {
+        const long long total = (long long)T * (D >> 3), want = (total + 255) / 256;
+        const int blocks = (int)(want < 65535LL * 4 ? want : 65535LL * 4);
+        if (dtype == FE_F32)
+            fe::launch(token_shift_vec_kernel<float>, blocks, 256, 0, stream, (const float*)h, mu, kept, kept_stride, seats, cu_q, token_req,
+                       (float*)out, T, D, n_seats);
+        else
+            fe::launch(token_shift_vec_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)h, mu, kept, kept_stride, seats, cu_q, token_req,
+                       (bf16*)out, T, D, n_seats);
+        return fe_check_launch("token_shift");
+    }
     const int threads = D >= 1024 ? 256 : 128;
     const int stretches = T >= 512 ? 1 : (D + threads - 1) / threads;
     const dim3 grid(T, stretches < 65535 ? stretches : 65535);
@@ -523,7 +574,7 @@ __device__ __forceinline__ GruStep gru_step(float zl, float xl, float bz, float 
     const float cand = u >= 0.f ? u + 0.5f : sigmoidf(u);
     return GruStep{1.f - z, z * cand};
 }
-__device__ __forceinline__ float silu(float g) { return g / (1.f + expf(-g)); }
+__device__ __forceinline__ float silu(float g) { return g * sigmoidf(g); }
 
 constexpr int GRU_AHEAD = 8;         // tokens whose values are asked for together: the chain of S waits for memory once per 8
 

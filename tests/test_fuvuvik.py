@@ -38,7 +38,7 @@ F64 = torch.float64
 
 def attention(heads, kv_heads, dim, vdim, conv, rot_dims, base=10000.0, scale=None):
     return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv,
-                                           "rot": {"base": base, "dims": rot_dims}, "scale": scale if scale is not None else 4.0 / dim ** 0.5}}
+                                           "rot": {"base": base, "dims": rot_dims}, "scale": scale if scale is not None else 2.0 / dim ** 0.5}}
 
 
 def chunked(heads, kv_heads, dim, vdim, size, rot_dims, base=10000.0, scale=None):
@@ -261,10 +261,11 @@ def test_stream_norm_and_update_alone(device, dtype, streams, width):
 
 
 @pytest.mark.parametrize("device,dtype", CASES)
-def test_token_shift_alone(device, dtype):
+@pytest.mark.parametrize("width", [24, 30])
+def test_token_shift_alone(device, dtype, width):
     from flexengine_b200.parts.streams import TokenShift
     dt = getattr(torch, dtype)
-    D, T = 24, 19
+    D, T = width, 19
     mu = randn(D, seed=1)
     h = randn(T, D, seed=2)
     shift = TokenShift(D, 0, 1)
