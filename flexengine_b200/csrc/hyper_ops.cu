@@ -137,7 +137,9 @@ template <> struct Quad<bf16> {
     }
 };
 
-template <typename T, int SMAX>
+// ITERS > 0: the row takes at most ITERS rounds of the block, and a thread asks for everything it reads of the row before it
+// works on any of it (the kernel waits for memory, not for arithmetic); ITERS == 0: any width, round by round.
+template <typename T, int SMAX, int ITERS>
 __global__ void stream_rmsnorm_vec_kernel(float* __restrict__ x, int S, int T_tokens, int H, const float* __restrict__ read,
                                           const float* __restrict__ weight, float eps, const T* __restrict__ y,
                                           const T* __restrict__ gate, const float* __restrict__ gate_bias,
@@ -153,27 +155,23 @@ __global__ void stream_rmsnorm_vec_kernel(float* __restrict__ x, int S, int T_to
         s_write[e] = write ? write[e] : 0.f;
         s_read[e] = read ? read[e] : 1.f;
     }
-    __syncthreads();
     const int i = blockIdx.x;
     int r = rows ? rows[i] : i;
     if (r < 0 || r >= T_tokens) r = 0;              // guarded: rows are checked on the host
     const size_t plane = (size_t)T_tokens * H;
     float* base = x + (size_t)r * H;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
     float ss = 0.f;
-    for (int j = threadIdx.x * 4; j < H; j += blockDim.x * 4) {
-        float4 v[SMAX];
-#pragma unroll
-        for (int s = 0; s < SMAX; ++s) v[s] = s < S ? Quad<float>::load(base + s * plane + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+    // columns j .. j + 3 of the row: the streams' values v, and of what goes into them y, gate and the gate's bias
+    auto columns = [&](int j, const float4* v, float4 yy, float4 gg, float4 bb) {
+        float4 u = zero;
         if (y) {
-            const float4 yy = Quad<T>::load(y + (size_t)r * H + j), gg = Quad<T>::load(gate + (size_t)r * H + j);
-            const float4 bb = Quad<float>::load(gate_bias + j);
             const float4 g = make_float4(yy.x * sigmoidf(gg.x + bb.x), yy.y * sigmoidf(gg.y + bb.y), yy.z * sigmoidf(gg.z + bb.z),
                                          yy.w * sigmoidf(gg.w + bb.w));
 #pragma unroll
             for (int t = 0; t < SMAX; ++t) {
                 if (t < S) {
-                    float4 n = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float4 n = zero;
 #pragma unroll
                     for (int s = 0; s < SMAX; ++s) {
                         if (s < S) {
@@ -198,6 +196,35 @@ __global__ void stream_rmsnorm_vec_kernel(float* __restrict__ x, int S, int T_to
         }
         *reinterpret_cast<float4*>(u_row + j) = u;
         ss += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+    };
+    if (ITERS > 0) {
+        constexpr int N = ITERS > 0 ? ITERS : 1;
+        float4 v[N][SMAX], yy[N], gg[N], bb[N];
+#pragma unroll
+        for (int it = 0; it < N; ++it) {
+            const int j = (it * blockDim.x + threadIdx.x) * 4;
+            const bool in = j < H;
+#pragma unroll
+            for (int s = 0; s < SMAX; ++s) v[it][s] = (in && s < S) ? Quad<float>::load(base + s * plane + j) : zero;
+            yy[it] = (in && y) ? Quad<T>::load(y + (size_t)r * H + j) : zero;
+            gg[it] = (in && y) ? Quad<T>::load(gate + (size_t)r * H + j) : zero;
+            bb[it] = (in && y) ? Quad<float>::load(gate_bias + j) : zero;
+        }
+        __syncthreads();                             // the mixing weights are in shared memory
+#pragma unroll
+        for (int it = 0; it < N; ++it) {
+            const int j = (it * blockDim.x + threadIdx.x) * 4;
+            if (j < H) columns(j, v[it], yy[it], gg[it], bb[it]);
+        }
+    } else {
+        __syncthreads();
+        for (int j = threadIdx.x * 4; j < H; j += blockDim.x * 4) {
+            float4 v[SMAX];
+#pragma unroll
+            for (int s = 0; s < SMAX; ++s) v[s] = s < S ? Quad<float>::load(base + s * plane + j) : zero;
+            const float4 yy = y ? Quad<T>::load(y + (size_t)r * H + j) : zero, gg = y ? Quad<T>::load(gate + (size_t)r * H + j) : zero;
+            columns(j, v, yy, gg, y ? Quad<float>::load(gate_bias + j) : zero);
+        }
     }
     const float total = block_sum(ss, scratch);
     const float inv = rsqrtf(total / (float)H + eps);
@@ -213,24 +240,37 @@ static int launch_stream_rmsnorm(float* x, int S, int T_tokens, int H, const flo
                                  const void* gate, const float* gate_bias, const float* mix, const float* write, const int* rows,
                                  int n_out, void* out, cudaStream_t stream) {
     const size_t smem = (size_t)H * sizeof(float);
-    // four columns a thread when every row, of the streams and of what goes into them, starts on a 16-byte boundary
+    // four columns a thread when every row, of the streams and of what goes into them, starts on a 16-byte boundary; with up
+    // to four streams and rows of up to 8,192 columns a thread takes its columns in at most two rounds, loaded together
     const bool vec = H % 4 == 0 && S <= 8 && (((size_t)x | (size_t)weight | (size_t)gate_bias) & 15) == 0 &&
                      (((size_t)y | (size_t)gate | (size_t)out) & 15) == 0;
-    const int threads = vec ? (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
-#define FE_LAUNCH_STREAM_NORM(KERNEL, SMAX)                                                                               \
-    fe::launch(KERNEL<T, SMAX>, n_out, threads, smem, stream, x, S, T_tokens, H, read, weight, eps,                      \
+    const bool staged = vec && S <= 4 && H <= 8192;
+    int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (vec) threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    if (staged) {
+        threads = ((H + 7) / 8 + 31) / 32 * 32;      // two rounds of four columns
+        if (threads < 64) threads = 64;
+    }
+#define FE_LAUNCH_STREAM_NORM_PLAIN(SMAX)                                                                                 \
+    fe::launch(stream_rmsnorm_kernel<T, SMAX>, n_out, threads, smem, stream, x, S, T_tokens, H, read, weight, eps,       \
                (const T*)y, (const T*)gate, gate_bias, mix, write, rows, (T*)out)
-    if (vec) {
-        if (S <= 1) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_vec_kernel, 1);
-        else if (S <= 2) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_vec_kernel, 2);
-        else if (S <= 4) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_vec_kernel, 4);
-        else FE_LAUNCH_STREAM_NORM(stream_rmsnorm_vec_kernel, 8);
-    } else if (S <= 1) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_kernel, 1);
-    else if (S <= 2) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_kernel, 2);
-    else if (S <= 4) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_kernel, 4);
-    else if (S <= 8) FE_LAUNCH_STREAM_NORM(stream_rmsnorm_kernel, 8);
-    else FE_LAUNCH_STREAM_NORM(stream_rmsnorm_kernel, 16);
-#undef FE_LAUNCH_STREAM_NORM
+#define FE_LAUNCH_STREAM_NORM_VEC(SMAX, ITERS)                                                                            \
+    fe::launch(stream_rmsnorm_vec_kernel<T, SMAX, ITERS>, n_out, threads, smem, stream, x, S, T_tokens, H, read, weight, \
+               eps, (const T*)y, (const T*)gate, gate_bias, mix, write, rows, (T*)out)
+    if (staged) {
+        if (S <= 1) FE_LAUNCH_STREAM_NORM_VEC(1, 2);
+        else if (S <= 2) FE_LAUNCH_STREAM_NORM_VEC(2, 2);
+        else FE_LAUNCH_STREAM_NORM_VEC(4, 2);
+    } else if (vec) {
+        if (S <= 4) FE_LAUNCH_STREAM_NORM_VEC(4, 0);
+        else FE_LAUNCH_STREAM_NORM_VEC(8, 0);
+    } else if (S <= 1) FE_LAUNCH_STREAM_NORM_PLAIN(1);
+    else if (S <= 2) FE_LAUNCH_STREAM_NORM_PLAIN(2);
+    else if (S <= 4) FE_LAUNCH_STREAM_NORM_PLAIN(4);
+    else if (S <= 8) FE_LAUNCH_STREAM_NORM_PLAIN(8);
+    else FE_LAUNCH_STREAM_NORM_PLAIN(16);
+#undef FE_LAUNCH_STREAM_NORM_PLAIN
+#undef FE_LAUNCH_STREAM_NORM_VEC
     return fe_check_launch("stream_rmsnorm");
 }
 
@@ -347,16 +387,82 @@ extern "C" int fe_token_shift(const void* h, const float* mu, float* kept, long 
 
 // ---------------------------------------------------------------------------------------------
 // Between the projection and the scores.  ``proj`` [T, ld] holds q | k | v of every token: ``heads`` query heads and
-// ``kv_heads`` key heads of ``dim`` entries, ``kv_heads`` value heads of ``vdim``.  One warp per (token, head of q, k or v):
+// ``kv_heads`` key heads of ``dim`` entries, ``kv_heads`` value heads of ``vdim``.  One block per token; its warps share out
+// the token's heads of q, k and v:
 //   convolution (taps > 0): y_t[c] = sum_j conv[c, j] * u_(t - taps + 1 + j)[c] over the request's own rows, those before
 //     this step from ``history`` [seats, (taps - 1) * C] (oldest first; zeros for a seat below 0);
-//   rotation (q, k): entries i and i + rot/2 of the head's first ``rot`` turn by position * inv_freq[i];
+//   rotation (q, k): entries i and i + rot/2 of the head's first ``rot`` turn by position * inv_freq[i]; the token's sines
+//     and cosines are worked out once, by the whole block, for all of its heads;
 //   unit norm (q, k; qk_norm): the head divided by sqrt(mean of its squares + eps);
 //   q into ``q_out`` [T, heads * head], k and v into their cache slots [pages, kv_heads, ps, head], zeros beyond dim / vdim.
-// The history of a channel is read only by the first taps - 1 tokens of the request's portion.  The warp of the portion's
-// first token therefore runs all of them for its head, one after the other, and then brings the history of its channels up to
-// date (the warps of the other early tokens do nothing), so that no warp reads what another one writes.
-template <typename T>
+// The history of a channel is read only by the first taps - 1 tokens of the request's portion.  The block of the portion's
+// first token therefore runs all of them, one after the other, and then brings the history up to date (the blocks of the
+// other early tokens do nothing), so that no block reads what another one writes.
+// PER > 0: a head's size is 32 * PER and a lane owns PER consecutive entries, moved with one load and one store each (rows
+// start on 16-byte boundaries); PER == 0: any size, entry c = lane + 32 k.
+namespace {
+
+template <typename T, int PER> struct Lanes;          // PER consecutive elements of T as floats
+template <int PER> struct Lanes<float, PER> {
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) v[i] = p[i];
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) p[i] = v[i];
+    }
+};
+template <> struct Lanes<float, 4> {
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Lanes<float, 8> {
+    static __device__ __forceinline__ void load(const float* p, float* v) { load8<float>(p, v); }
+    static __device__ __forceinline__ void store(float* p, const float* v) { store8<float>(p, v); }
+};
+template <int PER> struct Lanes<bf16, PER> {
+    static __device__ __forceinline__ void load(const bf16* p, float* v) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) v[i] = __bfloat162float(p[i]);
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float* v) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) p[i] = __float2bfloat16_rn(v[i]);
+    }
+};
+template <> struct Lanes<bf16, 2> {
+    static __device__ __forceinline__ void load(const bf16* p, float* v) {
+        const unsigned raw = *reinterpret_cast<const unsigned*>(p);
+        v[0] = __uint_as_float(raw << 16); v[1] = __uint_as_float(raw & 0xffff0000u);
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float* v) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]); }
+};
+template <> struct Lanes<bf16, 4> {
+    static __device__ __forceinline__ void load(const bf16* p, float* v) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
+        v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float* v) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const unsigned*>(&a);
+        raw.y = *reinterpret_cast<const unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+template <> struct Lanes<bf16, 8> {
+    static __device__ __forceinline__ void load(const bf16* p, float* v) { load8<bf16>(p, v); }
+    static __device__ __forceinline__ void store(bf16* p, const float* v) { store8<bf16>(p, v); }
+};
+
+}  // namespace
+
+template <typename T, int PER>
 __global__ void qkv_conv_rope_norm_cache_kernel(const T* __restrict__ proj, long long ld, const float* __restrict__ conv, float* history,
                                                 long long history_stride, int taps, const int* __restrict__ seats,
                                                 const int* __restrict__ cu_q, const int* __restrict__ token_req,
@@ -367,18 +473,15 @@ __global__ void qkv_conv_rope_norm_cache_kernel(const T* __restrict__ proj, long
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ float staged[];
-    const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
+    constexpr int LIMIT = PER > 0 ? PER : 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int half = rot >> 1;
+    float* cosines = staged;                               // [half], then the sines [half], then a head per warp
+    float* sines = staged + half;
+    float* buf = staged + rot + (size_t)warp * head;
     const int per_token = heads + 2 * kv_heads;
-    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + warp_in_block;
-    if (warp >= (long long)T_tokens * per_token) return;
-    const int tok = (int)(warp / per_token), hs = (int)(warp % per_token);
-    float* buf = staged + (size_t)warp_in_block * head;
+    const int tok = blockIdx.x;
     const int C = (heads + kv_heads) * dim + kv_heads * vdim;
-    // which head this is: 0 query, 1 key, 2 value; its first channel and its size
-    const int what = hs < heads ? 0 : (hs < heads + kv_heads ? 1 : 2);
-    const int index = what == 0 ? hs : (what == 1 ? hs - heads : hs - heads - kv_heads);
-    const int hd = what == 2 ? vdim : dim;
-    const int ch0 = what == 0 ? index * dim : (what == 1 ? (heads + index) * dim : (heads + kv_heads) * dim + index * vdim);
     const int r = token_req[tok];
     const int first = cu_q[r], n = cu_q[r + 1] - first, li = tok - first;
     const int seat = seats[r];
@@ -391,73 +494,130 @@ __global__ void qkv_conv_rope_norm_cache_kernel(const T* __restrict__ proj, long
     }
     for (int rep = 0; rep < reps; ++rep) {
         const int t = tok + rep, lt = li + rep;
-        for (int c = lane; c < hd; c += 32) {
-            const int ch = ch0 + c;
-            float acc;
-            if (conv) {
-                acc = 0.f;
-                for (int j = 0; j < taps; ++j) {
-                    const int from = lt - (taps - 1 - j);
-                    float u = 0.f;
-                    if (from >= 0) u = to_float(proj[(size_t)(first + from) * ld + ch]);
-                    else if (hist) u = hist[(size_t)(back + from) * C + ch];
-                    acc = fmaf(conv[(size_t)ch * taps + j], u, acc);
-                }
-            } else {
-                acc = to_float(proj[(size_t)t * ld + ch]);
-            }
-            buf[c] = acc;
+        if (inv_freq && rot > 0) {
+            const float pos = (float)positions[t];
+            for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &sines[i], &cosines[i]);
         }
-        __syncwarp();
-        float inv = 1.f;
-        if (what != 2) {
-            if (inv_freq && rot > 0) {
-                const float pos = (float)positions[t];
-                const int half = rot >> 1;
-                for (int i = lane; i < half; i += 32) {
-                    float s, c;
-                    sincosf(pos * inv_freq[i], &s, &c);
-                    const float a = buf[i], b = buf[i + half];
-                    buf[i] = a * c - b * s;
-                    buf[i + half] = b * c + a * s;
-                }
-                __syncwarp();
-            }
-            if (qk_norm) {
-                float ss = 0.f;
-                for (int c = lane; c < hd; c += 32) ss = fmaf(buf[c], buf[c], ss);
-                ss = warp_sum(ss);
-                inv = rsqrtf(ss / (float)hd + eps);
-            }
-        }
-        T* dst = nullptr;
-        if (what == 0) {
-            dst = q_out + (size_t)t * heads * head + (size_t)index * head;
-        } else if (slot_mapping) {
-            const int slot = slot_mapping[t];
-            if (slot >= 0) {
-                if (slot >= num_slots) {
-                    if (lane == 0 && status) atomicOr(status, FE_STATUS_BAD_SLOT);
+        __syncthreads();
+        for (int hs = warp; hs < per_token; hs += warps) {
+            // which head this is: 0 query, 1 key, 2 value; its first channel and its size
+            const int what = hs < heads ? 0 : (hs < heads + kv_heads ? 1 : 2);
+            const int index = what == 0 ? hs : (what == 1 ? hs - heads : hs - heads - kv_heads);
+            const int hd = what == 2 ? vdim : dim;
+            const int ch0 = what == 0 ? index * dim : (what == 1 ? (heads + index) * dim : (heads + kv_heads) * dim + index * vdim);
+            // this lane's entries: PER consecutive ones from lane * PER, or lane, lane + 32, ...
+            const int rounds = PER > 0 ? 1 : (hd + 31) / 32;
+            for (int k = 0; k < rounds; ++k) {
+                const int c = PER > 0 ? lane * PER : lane + 32 * k;
+                if (c >= hd) continue;
+                const int ch = ch0 + c;
+                float acc[LIMIT];
+                if (conv) {
+#pragma unroll
+                    for (int e = 0; e < LIMIT; ++e) acc[e] = 0.f;
+                    for (int j = 0; j < taps; ++j) {
+                        const int from = lt - (taps - 1 - j);
+                        float u[LIMIT];
+                        if (from >= 0) Lanes<T, LIMIT>::load(proj + (size_t)(first + from) * ld + ch, u);
+                        else if (hist) Lanes<float, LIMIT>::load(hist + (size_t)(back + from) * C + ch, u);
+                        else {
+#pragma unroll
+                            for (int e = 0; e < LIMIT; ++e) u[e] = 0.f;
+                        }
+#pragma unroll
+                        for (int e = 0; e < LIMIT; ++e) acc[e] = fmaf(conv[(size_t)(ch + e) * taps + j], u[e], acc[e]);
+                    }
                 } else {
-                    const long long page = slot / ps, off = slot % ps;
-                    dst = (what == 1 ? kc : vc) + ((page * kv_heads + index) * ps + off) * head;
+                    Lanes<T, LIMIT>::load(proj + (size_t)t * ld + ch, acc);
+                }
+#pragma unroll
+                for (int e = 0; e < LIMIT; ++e) buf[c + e] = acc[e];
+            }
+            __syncwarp();
+            float inv = 1.f;
+            if (what != 2) {
+                if (inv_freq && rot > 0) {
+                    for (int i = lane; i < half; i += 32) {
+                        const float s = sines[i], c = cosines[i];
+                        const float a = buf[i], b = buf[i + half];
+                        buf[i] = a * c - b * s;
+                        buf[i + half] = b * c + a * s;
+                    }
+                    __syncwarp();
+                }
+                if (qk_norm) {
+                    float ss = 0.f;
+                    for (int c = lane; c < hd; c += 32) ss = fmaf(buf[c], buf[c], ss);
+                    ss = warp_sum(ss);
+                    inv = rsqrtf(ss / (float)hd + eps);
                 }
             }
+            T* dst = nullptr;
+            if (what == 0) {
+                dst = q_out + (size_t)t * heads * head + (size_t)index * head;
+            } else if (slot_mapping) {
+                const int slot = slot_mapping[t];
+                if (slot >= 0) {
+                    if (slot >= num_slots) {
+                        if (lane == 0 && status) atomicOr(status, FE_STATUS_BAD_SLOT);
+                    } else {
+                        const long long page = slot / ps, off = slot % ps;
+                        dst = (what == 1 ? kc : vc) + ((page * kv_heads + index) * ps + off) * head;
+                    }
+                }
+            }
+            if (dst) {
+                if (PER > 0) {
+                    float v[LIMIT];
+#pragma unroll
+                    for (int e = 0; e < LIMIT; ++e) v[e] = buf[lane * LIMIT + e] * inv;
+                    Lanes<T, LIMIT>::store(dst + lane * LIMIT, v);
+                    for (int c = hd + lane; c < head; c += 32) dst[c] = from_float<T>(0.f);
+                } else {
+                    for (int c = lane; c < head; c += 32) dst[c] = from_float<T>(c < hd ? buf[c] * inv : 0.f);
+                }
+            }
+            __syncwarp();
         }
-        if (dst)
-            for (int c = lane; c < head; c += 32) dst[c] = from_float<T>(c < hd ? buf[c] * inv : 0.f);
-        __syncwarp();
+        __syncthreads();                 // before the next token's sines and cosines go where these are
     }
     if (hist && li == 0) {
         // the last ``back`` projected rows of the request, oldest first: what was kept moves up, this step's rows follow
-        for (int c = lane; c < hd; c += 32) {
-            const int ch = ch0 + c;
+        for (int ch = threadIdx.x; ch < C; ch += blockDim.x) {
             for (int m = 0; m < back; ++m) {
                 const int from = m + n;
                 hist[(size_t)m * C + ch] = from < back ? hist[(size_t)from * C + ch] : to_float(proj[(size_t)(first + from - back) * ld + ch]);
             }
         }
     }
+}
+
+template <typename T>
+static int launch_qkv_prepare(const void* proj, long long ld, const float* conv, float* history, long long history_stride, int taps,
+                              const int* seats, const int* cu_q, const int* token_req, const int* positions, const float* inv_freq, int rot,
+                              int qk_norm, float eps, const int* slot_mapping, void* kc, void* vc, void* q_out, int T_tokens, int heads,
+                              int kv_heads, int dim, int vdim, int head, int ps, long long num_slots, int n_seats, int* status,
+                              cudaStream_t stream) {
+    const int per_token = heads + 2 * kv_heads;
+    const int warps = per_token >= 8 ? 8 : (per_token >= 4 ? 4 : per_token);
+    const size_t smem = ((size_t)rot + (size_t)warps * head) * sizeof(float);
+    // a lane owns consecutive entries when both head sizes are the same multiple of 32 and every row it touches starts on a
+    // 16-byte boundary
+    const long long C = (long long)(heads + kv_heads) * dim + (long long)kv_heads * vdim;
+    const bool aligned = dim == vdim && dim % 32 == 0 && dim <= 256 && ld % 8 == 0 && head % 8 == 0 && C % 4 == 0 && history_stride % 4 == 0 &&
+                         (((size_t)proj | (size_t)kc | (size_t)vc | (size_t)q_out | (size_t)history) & 15) == 0;
+    const int per = aligned ? dim / 32 : 0;
+#define FE_LAUNCH_QKV_PREPARE(PER)                                                                                                   \
+    fe::launch(qkv_conv_rope_norm_cache_kernel<T, PER>, T_tokens, warps * 32, smem, stream, (const T*)proj, ld, conv, history,     \
+               history_stride, taps, seats, cu_q, token_req, positions, inv_freq, rot, qk_norm, eps, slot_mapping, (T*)kc, (T*)vc,  \
+               (T*)q_out, T_tokens, heads, kv_heads, dim, vdim, head, ps, num_slots, n_seats, status)
+    if (per == 1) FE_LAUNCH_QKV_PREPARE(1);
+    else if (per == 2) FE_LAUNCH_QKV_PREPARE(2);
+    else if (per == 4) FE_LAUNCH_QKV_PREPARE(4);
+    else if (per == 8) FE_LAUNCH_QKV_PREPARE(8);
+    else FE_LAUNCH_QKV_PREPARE(0);
+#undef FE_LAUNCH_QKV_PREPARE
+    return fe_check_launch("qkv_conv_rope_norm_cache");
 }
 
 extern "C" int fe_qkv_conv_rope_norm_cache(const void* proj, long long ld, const float* conv, float* history, long long history_stride,
@@ -473,22 +633,15 @@ extern "C" int fe_qkv_conv_rope_norm_cache(const void* proj, long long ld, const
     const long long C = (long long)(heads + kv_heads) * dim + (long long)kv_heads * vdim;
     FE_REQUIRE(ld >= C && (taps <= 1 || history_stride >= (taps - 1) * C), "qkv_conv_rope_norm_cache: rows too short");
     if (T == 0) return 0;
-    const int warps = 4;
-    const long long total = (long long)T * (heads + 2 * kv_heads);
-    const long long blocks = (total + warps - 1) / warps;
-    FE_REQUIRE(blocks <= 2147483647LL, "qkv_conv_rope_norm_cache: grid too large");
-    const size_t smem = (size_t)warps * head * sizeof(float);
     if (dtype == FE_F32)
-        fe::launch(qkv_conv_rope_norm_cache_kernel<float>, (unsigned)blocks, warps * 32, smem, stream, (const float*)proj, ld, conv, history,
-                   history_stride, taps, seats, cu_q, token_req, positions, inv_freq, rot, qk_norm, eps, slot_mapping, (float*)kc,
-                   (float*)vc, (float*)q_out, T, heads, kv_heads, dim, vdim, head, ps, num_slots, n_seats, status);
-    else if (dtype == FE_BF16)
-        fe::launch(qkv_conv_rope_norm_cache_kernel<bf16>, (unsigned)blocks, warps * 32, smem, stream, (const bf16*)proj, ld, conv, history,
-                   history_stride, taps, seats, cu_q, token_req, positions, inv_freq, rot, qk_norm, eps, slot_mapping, (bf16*)kc,
-                   (bf16*)vc, (bf16*)q_out, T, heads, kv_heads, dim, vdim, head, ps, num_slots, n_seats, status);
-    else
-        FE_REQUIRE(false, "qkv_conv_rope_norm_cache: unknown dtype %d", dtype);
-    return fe_check_launch("qkv_conv_rope_norm_cache");
+        return launch_qkv_prepare<float>(proj, ld, conv, history, history_stride, taps, seats, cu_q, token_req, positions, inv_freq, rot,
+                                         qk_norm, eps, slot_mapping, kc, vc, q_out, T, heads, kv_heads, dim, vdim, head, ps, num_slots,
+                                         n_seats, status, stream);
+    if (dtype == FE_BF16)
+        return launch_qkv_prepare<bf16>(proj, ld, conv, history, history_stride, taps, seats, cu_q, token_req, positions, inv_freq, rot,
+                                        qk_norm, eps, slot_mapping, kc, vc, q_out, T, heads, kv_heads, dim, vdim, head, ps, num_slots,
+                                        n_seats, status, stream);
+    FE_REQUIRE(false, "qkv_conv_rope_norm_cache: unknown dtype %d", dtype);
 }
 
 // ---------------------------------------------------------------------------------------------
