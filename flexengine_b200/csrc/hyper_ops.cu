@@ -389,8 +389,9 @@ extern "C" int fe_token_shift(const void* h, const float* mu, float* kept, long 
 // Between the projection and the scores.  ``proj`` [T, ld] holds q | k | v of every token: ``heads`` query heads and
 // ``kv_heads`` key heads of ``dim`` entries, ``kv_heads`` value heads of ``vdim``.  One block per token; its warps share out
 // the token's heads of q, k and v:
-//   convolution (taps > 0): y_t[c] = sum_j conv[c, j] * u_(t - taps + 1 + j)[c] over the request's own rows, those before
-//     this step from ``history`` [seats, (taps - 1) * C] (oldest first; zeros for a seat below 0);
+//   convolution (taps > 0): y_t[c] = sum_j conv[j, c] * u_(t - taps + 1 + j)[c] over the request's own rows, those before
+//     this step from ``history`` [seats, (taps - 1) * C] (oldest first; zeros for a seat below 0); the table is held tap by
+//     tap, [taps, C], so that the lanes of a warp read neighbouring numbers;
 //   rotation (q, k): entries i and i + rot/2 of the head's first ``rot`` turn by position * inv_freq[i]; the token's sines
 //     and cosines are worked out once, by the whole block, for all of its heads;
 //   unit norm (q, k; qk_norm): the head divided by sqrt(mean of its squares + eps);
@@ -515,9 +516,12 @@ __global__ void qkv_conv_rope_norm_cache_kernel(const T* __restrict__ proj, long
                 if (conv) {
 #pragma unroll
                     for (int e = 0; e < LIMIT; ++e) acc[e] = 0.f;
+                    // four taps at a time: their loads are all on their way before the first is used
+#pragma unroll 4
                     for (int j = 0; j < taps; ++j) {
                         const int from = lt - (taps - 1 - j);
-                        float u[LIMIT];
+                        float u[LIMIT], w[LIMIT];
+                        Lanes<float, LIMIT>::load(conv + (size_t)j * C + ch, w);
                         if (from >= 0) Lanes<T, LIMIT>::load(proj + (size_t)(first + from) * ld + ch, u);
                         else if (hist) Lanes<float, LIMIT>::load(hist + (size_t)(back + from) * C + ch, u);
                         else {
@@ -525,7 +529,7 @@ __global__ void qkv_conv_rope_norm_cache_kernel(const T* __restrict__ proj, long
                             for (int e = 0; e < LIMIT; ++e) u[e] = 0.f;
                         }
 #pragma unroll
-                        for (int e = 0; e < LIMIT; ++e) acc[e] = fmaf(conv[(size_t)(ch + e) * taps + j], u[e], acc[e]);
+                        for (int e = 0; e < LIMIT; ++e) acc[e] = fmaf(w[e], u[e], acc[e]);
                     }
                 } else {
                     Lanes<T, LIMIT>::load(proj + (size_t)t * ld + ch, acc);
@@ -599,13 +603,17 @@ static int launch_qkv_prepare(const void* proj, long long ld, const float* conv,
                               int kv_heads, int dim, int vdim, int head, int ps, long long num_slots, int n_seats, int* status,
                               cudaStream_t stream) {
     const int per_token = heads + 2 * kv_heads;
-    const int warps = per_token >= 8 ? 8 : (per_token >= 4 ? 4 : per_token);
+    // up to 16 warps share out the token's heads evenly: 24 heads are two rounds of 12 warps
+    const int rounds = (per_token + 15) / 16;
+    int warps = (per_token + rounds - 1) / rounds;
+    const int fit = (int)((48 * 1024 - (size_t)rot * sizeof(float)) / ((size_t)head * sizeof(float)));      // a head per warp in shared memory
+    if (warps > fit) warps = fit;
     const size_t smem = ((size_t)rot + (size_t)warps * head) * sizeof(float);
     // a lane owns consecutive entries when both head sizes are the same multiple of 32 and every row it touches starts on a
     // 16-byte boundary
     const long long C = (long long)(heads + kv_heads) * dim + (long long)kv_heads * vdim;
     const bool aligned = dim == vdim && dim % 32 == 0 && dim <= 256 && ld % 8 == 0 && head % 8 == 0 && C % 4 == 0 && history_stride % 4 == 0 &&
-                         (((size_t)proj | (size_t)kc | (size_t)vc | (size_t)q_out | (size_t)history) & 15) == 0;
+                         (((size_t)proj | (size_t)kc | (size_t)vc | (size_t)q_out | (size_t)history | (size_t)conv) & 15) == 0;
     const int per = aligned ? dim / 32 : 0;
 #define FE_LAUNCH_QKV_PREPARE(PER)                                                                                                   \
     fe::launch(qkv_conv_rope_norm_cache_kernel<T, PER>, T_tokens, warps * 32, smem, stream, (const T*)proj, ld, conv, history,     \

@@ -720,7 +720,7 @@ def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, 
                              qk_norm, eps, slot_mapping, k_cache, v_cache, heads, kv_heads, dim, vdim, head, page_size):
     """What attention does between its projection and its scores, in one kernel (csrc/hyper_ops.cu).  ``projected``
     [T, >= channels] holds q | k | v (``heads`` and ``kv_heads`` heads of ``dim``, ``kv_heads`` of ``vdim``).  A causal
-    convolution of ``taps`` taps over time per channel (``conv`` [channels, taps] float32, None for none; ``history``
+    convolution of ``taps`` taps over time per channel (``conv`` [taps, channels] float32, tap by tap, None for none; ``history``
     [seats, (taps - 1) channels] float32 holds every request's last taps - 1 projected rows and is brought up to date), the
     first ``rot_dims`` entries of every query and key head turned by position * inv_freq (pairs i, i + rot_dims/2), queries
     and keys divided by their root mean square (``qk_norm``), keys and values into their cache slots
@@ -734,8 +734,8 @@ def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, 
     if k_cache.dtype != projected.dtype or tuple(k_cache.shape[1:]) != (kv_heads, page_size, head) or not k_cache.is_contiguous() \
             or not v_cache.is_contiguous() or v_cache.shape != k_cache.shape:
         raise ValueError("qkv_conv_rope_norm_cache: caches are contiguous [pages, kv_heads, page_size, head] in the compute dtype")
-    if conv is not None and (conv.dtype != torch.float32 or tuple(conv.shape) != (channels, taps) or not conv.is_contiguous()):
-        raise ValueError("qkv_conv_rope_norm_cache: conv is contiguous float32 [channels, taps]")
+    if conv is not None and (conv.dtype != torch.float32 or tuple(conv.shape) != (taps, channels) or not conv.is_contiguous()):
+        raise ValueError("qkv_conv_rope_norm_cache: conv is contiguous float32 [taps, channels]")
     if conv is None:
         taps = 0
     if taps > 1 and (history is None or history.dtype != torch.float32 or history.stride(-1) != 1

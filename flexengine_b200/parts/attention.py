@@ -125,6 +125,7 @@ class GatedAttentionMixer(Mixer):
         if self.head > 1024:
             raise ValueError(f"head size {self.head}: the attention kernels take up to 1024")
         self.qkvg_weight = self.conv_weight = self.o_weight = None
+        self._conv_by_tap = None
         self._inv_freq = {}
 
     @property
@@ -137,6 +138,11 @@ class GatedAttentionMixer(Mixer):
         if self.conv > 0:
             shapes["conv.weight"] = ((self.channels, self.conv), "vector")
         return shapes
+
+    def bind(self, tensors: dict) -> None:
+        super().bind(tensors)
+        # the table tap by tap, [taps, channels]: the kernel's lanes then read neighbouring numbers
+        self._conv_by_tap = self.conv_weight.t().contiguous() if self.conv > 0 else None
 
     def reads_first(self):
         return self.qkvg_weight
@@ -160,7 +166,7 @@ class GatedAttentionMixer(Mixer):
         history = ctx.groups[self.conv_group].state(self.conv_slot) if self.conv > 1 else None
         projected = ops.linear(h, self.qkvg_weight)                          # [T, channels + heads]
         queries = ops.qkv_conv_rope_norm_cache(
-            projected, self.conv_weight, history, self.conv, ctx.state_slots, ctx.cu_q, ctx.token_request, ctx.positions,
+            projected, self._conv_by_tap, history, self.conv, ctx.state_slots, ctx.cu_q, ctx.token_request, ctx.positions,
             self.inverse_frequencies(h.device) if self.rot_dims else None, self.rot_dims, self.qk_norm, self.eps, slot_mapping,
             k_cache, v_cache, self.heads, self.kv_heads, self.dim, self.vdim, self.head, group.page_size)
         # one int says what a query sees: 0 every earlier key, w > 0 the last w, -c < 0 its own chunk of c positions

@@ -180,7 +180,7 @@ def token_shift(h, mu, kept, state_slots, cu_q, token_request):
 def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, token_request, positions, inv_freq, rot_dims,
                              qk_norm, eps, slot_mapping, k_cache, v_cache, heads, kv_heads, dim, vdim, head, page_size):
     """projected [T, >= channels] holds q | k | v.  A causal convolution of ``taps`` taps over time per channel (``conv``
-    [channels, taps]; ``history`` [seats, (taps - 1) channels] holds every request's last taps - 1 projected rows and is
+    [taps, channels]; ``history`` [seats, (taps - 1) channels] holds every request's last taps - 1 projected rows and is
     brought up to date), rotation of the first ``rot_dims`` entries of the query and key heads, their unit norm, keys and
     values into the cache and the queries out, both padded with zeros to ``head`` entries a head."""
     T = projected.shape[0]
@@ -195,7 +195,7 @@ def qkv_conv_rope_norm_cache(projected, conv, history, taps, state_slots, cu_q, 
             old = history[seats[r]].view(back, C) if (seats[r] >= 0 and back) else torch.zeros(back, C, device=u.device)
             rows = torch.cat([old, u[a:b]])
             for j in range(taps):
-                y[a:b] += conv[:, j].float() * rows[j:j + (b - a)]
+                y[a:b] += conv[j].float() * rows[j:j + (b - a)]
             if seats[r] >= 0 and back:
                 history[seats[r]] = rows[rows.shape[0] - back:].reshape(-1)
         u = y
