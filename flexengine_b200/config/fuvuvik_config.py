@@ -78,7 +78,7 @@ class FuvuvikConfig:
                     heads=_get(entry, "mixer.heads", int), kv_heads=_get(entry, "mixer.kv_heads", int), dim=dim,
                     vdim=_get(entry, "mixer.vdim", int), scale=_get(entry, "mixer.scale", float),
                     rot_base=_get(entry, "mixer.rot.base", float), rot_dims=_get(entry, "mixer.rot.dims", int),
-                    conv=0 if chunked else _get(entry, "mixer.conv", int), qk_norm=not chunked,
+                    conv=0 if chunked else _get(entry, "mixer.conv", int, default=0, required=False), qk_norm=not chunked,
                     mask="chunk" if chunked else "full", mask_size=_get(entry, "mixer.mask.size", int) if chunked else 0,
                     sink=chunked)
                 if min(mixer.heads, mixer.kv_heads, mixer.dim, mixer.vdim) <= 0 or mixer.heads % mixer.kv_heads:
