@@ -346,6 +346,20 @@ def test_mingru_remembers_over_hundreds_of_tokens(device, dtype):
     close(got, want, dtype, "far memory", bars=(1e-4, 0.1))
 
 
+@pytest.mark.parametrize("device,dtype", CASES)
+def test_mingru_over_a_portion_of_thousands_of_tokens(device, dtype):
+    """A portion of 4,200 tokens (on the device: the scan in blocks of 64, chained) and what follows it, against the walk."""
+    dt = getattr(torch, dtype)
+    D, W, T = 16, 40, 4300
+    weights = mingru_weights(D, W, seed=17)
+    weights["z.b"] = torch.full((W,), -3.0)                                   # slow gates: the state spans many blocks
+    mixer, spec = mingru_part(D, W, weights, device, dt)
+    h = randn(T, D, seed=18)
+    want = plain.mingru_mixer(h.to(F64), as64(weights), "")
+    got = drive(lambda ctx, rows: mixer.forward(ctx, rows, RunEntry(0, 0, 0, True)), [spec], h, [4200, 98, 1, 1], device, dt)
+    close(got, want, dtype, "a long portion", bars=(1e-4, 0.1))
+
+
 def attention_weights(D, m, seed, conv):
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     w = {"q": randn(H * d, D, seed=seed, scale=D ** -0.5), "k": randn(G * d, D, seed=seed + 1, scale=D ** -0.5),
