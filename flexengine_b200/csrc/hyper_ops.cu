@@ -65,7 +65,9 @@ __global__ void stream_rmsnorm_kernel(float* __restrict__ x, int S, int T_tokens
                                       const float* __restrict__ weight, float eps, const T* __restrict__ y,
                                       const T* __restrict__ gate, const float* __restrict__ gate_bias,
                                       const float* __restrict__ mix, const float* __restrict__ write,
-                                      const int* __restrict__ rows, T* __restrict__ out) {
+                                      const int* __restrict__ rows, T* __restrict__ out, const float* __restrict__ shift_mu,
+                                      float* kept, long long kept_stride, const int* __restrict__ seats, int n_seats,
+                                      T* __restrict__ shifted) {
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ float u_row[];
@@ -113,7 +115,21 @@ __global__ void stream_rmsnorm_kernel(float* __restrict__ x, int S, int T_tokens
     const float total = block_sum(ss, scratch);
     const float inv = rsqrtf(total / (float)H + eps);
     T* o = out + (size_t)i * H;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_float<T>(u_row[j] * inv * weight[j]);
+    // ``shifted``: row i is request i's one token of the step; the token shift of the normed row is done here as well
+    float* mine = nullptr;
+    if (shifted) {
+        const int seat = seats[i];
+        if (seat >= 0 && seat < n_seats) mine = kept + (size_t)seat * kept_stride;
+    }
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const T v = from_float<T>(u_row[j] * inv * weight[j]);
+        o[j] = v;
+        if (shifted) {
+            const float x = to_float(v), before = mine ? mine[j] : 0.f;
+            shifted[(size_t)i * H + j] = from_float<T>(fmaf(before - x, shift_mu[j], x));
+            if (mine) mine[j] = x;
+        }
+    }
 }
 
 // The same, four columns a thread at a time (H % 4 == 0): 16-byte loads and stores of the float streams.
@@ -144,7 +160,9 @@ __global__ void stream_rmsnorm_vec_kernel(float* __restrict__ x, int S, int T_to
                                           const float* __restrict__ weight, float eps, const T* __restrict__ y,
                                           const T* __restrict__ gate, const float* __restrict__ gate_bias,
                                           const float* __restrict__ mix, const float* __restrict__ write,
-                                          const int* __restrict__ rows, T* __restrict__ out) {
+                                          const int* __restrict__ rows, T* __restrict__ out, const float* __restrict__ shift_mu,
+                                          float* kept, long long kept_stride, const int* __restrict__ seats, int n_seats,
+                                          T* __restrict__ shifted) {
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ float u_row[];
@@ -229,21 +247,37 @@ __global__ void stream_rmsnorm_vec_kernel(float* __restrict__ x, int S, int T_to
     const float total = block_sum(ss, scratch);
     const float inv = rsqrtf(total / (float)H + eps);
     T* o = out + (size_t)i * H;
+    // ``shifted``: row i is request i's one token of the step; the token shift of the normed row is done here as well (on the
+    // row as it was rounded, so that the kept row is what a later step reads of it)
+    float* mine = nullptr;
+    if (shifted) {
+        const int seat = seats[i];
+        if (seat >= 0 && seat < n_seats) mine = kept + (size_t)seat * kept_stride;
+    }
     for (int j = threadIdx.x * 4; j < H; j += blockDim.x * 4) {
         const float4 u = *reinterpret_cast<const float4*>(u_row + j), w = Quad<float>::load(weight + j);
         Quad<T>::store(o + j, make_float4(u.x * inv * w.x, u.y * inv * w.y, u.z * inv * w.z, u.w * inv * w.w));
+        if (shifted) {
+            const float4 x = Quad<T>::load(o + j), m = Quad<float>::load(shift_mu + j);
+            const float4 before = mine ? Quad<float>::load(mine + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            Quad<T>::store(shifted + (size_t)i * H + j, make_float4(fmaf(before.x - x.x, m.x, x.x), fmaf(before.y - x.y, m.y, x.y),
+                                                                      fmaf(before.z - x.z, m.z, x.z), fmaf(before.w - x.w, m.w, x.w)));
+            if (mine) Quad<float>::store(mine + j, x);
+        }
     }
 }
 
 template <typename T>
 static int launch_stream_rmsnorm(float* x, int S, int T_tokens, int H, const float* read, const float* weight, float eps, const void* y,
                                  const void* gate, const float* gate_bias, const float* mix, const float* write, const int* rows,
-                                 int n_out, void* out, cudaStream_t stream) {
+                                 int n_out, void* out, const float* shift_mu, float* kept, long long kept_stride, const int* seats,
+                                 int n_seats, void* shifted, cudaStream_t stream) {
     const size_t smem = (size_t)H * sizeof(float);
     // four columns a thread when every row, of the streams and of what goes into them, starts on a 16-byte boundary; with up
     // to four streams and rows of up to 8,192 columns a thread takes its columns in at most two rounds, loaded together
     const bool vec = H % 4 == 0 && S <= 8 && (((size_t)x | (size_t)weight | (size_t)gate_bias) & 15) == 0 &&
-                     (((size_t)y | (size_t)gate | (size_t)out) & 15) == 0;
+                     (((size_t)y | (size_t)gate | (size_t)out | (size_t)shifted | (size_t)shift_mu | (size_t)kept) & 15) == 0 &&
+                     kept_stride % 4 == 0;
     const bool staged = vec && S <= 4 && H <= 8192;
     int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (vec) threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
@@ -253,10 +287,12 @@ static int launch_stream_rmsnorm(float* x, int S, int T_tokens, int H, const flo
     }
 #define FE_LAUNCH_STREAM_NORM_PLAIN(SMAX)                                                                                 \
     fe::launch(stream_rmsnorm_kernel<T, SMAX>, n_out, threads, smem, stream, x, S, T_tokens, H, read, weight, eps,       \
-               (const T*)y, (const T*)gate, gate_bias, mix, write, rows, (T*)out)
+               (const T*)y, (const T*)gate, gate_bias, mix, write, rows, (T*)out, shift_mu, kept, kept_stride, seats, n_seats, \
+               (T*)shifted)
 #define FE_LAUNCH_STREAM_NORM_VEC(SMAX, ITERS)                                                                            \
     fe::launch(stream_rmsnorm_vec_kernel<T, SMAX, ITERS>, n_out, threads, smem, stream, x, S, T_tokens, H, read, weight, \
-               eps, (const T*)y, (const T*)gate, gate_bias, mix, write, rows, (T*)out)
+               eps, (const T*)y, (const T*)gate, gate_bias, mix, write, rows, (T*)out, shift_mu, kept, kept_stride, seats,       \
+               n_seats, (T*)shifted)
     if (staged) {
         if (S <= 1) FE_LAUNCH_STREAM_NORM_VEC(1, 2);
         else if (S <= 2) FE_LAUNCH_STREAM_NORM_VEC(2, 2);
@@ -274,17 +310,25 @@ static int launch_stream_rmsnorm(float* x, int S, int T_tokens, int H, const flo
     return fe_check_launch("stream_rmsnorm");
 }
 
+// ``shifted`` (may be null): a step in which row i is request i's one token; the token shift of the normed rows is then done
+// here too: shifted = h + (kept[seat] - h) * shift_mu, and the seat keeps h (``kept`` [seats, stride] float; a seat below 0 reads
+// zeros and keeps nothing).  Only with rows == nullptr.
 extern "C" int fe_stream_rmsnorm(float* x, int S, int T, int H, const float* read, const float* weight, float eps, const void* y,
                                  const void* gate, const float* gate_bias, const float* mix, const float* write, const int* rows,
-                                 int n_out, void* out, int dtype, cudaStream_t stream) {
+                                 int n_out, void* out, const float* shift_mu, float* kept, long long kept_stride, const int* seats,
+                                 int n_seats, void* shifted, int dtype, cudaStream_t stream) {
     FE_REQUIRE(S >= 1 && S <= MAX_STREAMS && T >= 0 && H > 0 && n_out >= 0, "stream_rmsnorm: bad sizes S=%d T=%d H=%d", S, T, H);
     FE_REQUIRE((size_t)H * sizeof(float) <= 48 * 1024, "stream_rmsnorm: rows of %d floats do not fit shared memory", H);
     FE_REQUIRE(y == nullptr || (gate && gate_bias && mix && write), "stream_rmsnorm: an update needs its gate, bias, mix and write");
+    FE_REQUIRE(shifted == nullptr || (rows == nullptr && shift_mu && kept && seats && kept_stride >= H && n_out == T),
+               "stream_rmsnorm: the token shift needs all rows, its weights, the kept rows and the seats");
     if (n_out == 0 || T == 0) return 0;
     if (dtype == FE_F32)
-        return launch_stream_rmsnorm<float>(x, S, T, H, read, weight, eps, y, gate, gate_bias, mix, write, rows, n_out, out, stream);
+        return launch_stream_rmsnorm<float>(x, S, T, H, read, weight, eps, y, gate, gate_bias, mix, write, rows, n_out, out, shift_mu, kept,
+                                            kept_stride, seats, n_seats, shifted, stream);
     if (dtype == FE_BF16)
-        return launch_stream_rmsnorm<bf16>(x, S, T, H, read, weight, eps, y, gate, gate_bias, mix, write, rows, n_out, out, stream);
+        return launch_stream_rmsnorm<bf16>(x, S, T, H, read, weight, eps, y, gate, gate_bias, mix, write, rows, n_out, out, shift_mu, kept,
+                                           kept_stride, seats, n_seats, shifted, stream);
     FE_REQUIRE(false, "stream_rmsnorm: unknown dtype %d", dtype);
 }
 

@@ -673,12 +673,16 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
 
 
 # ---- several residual streams, token shift, gated attention, minGRU ---------------------------------------------
-def stream_rmsnorm(streams, read, weight, eps, out_dtype, update=None, rows=None):
+FUSES_TOKEN_SHIFT = True        # stream_rmsnorm(..., shift=) does the token shift of a decode step's rows in the same kernel
+
+
+def stream_rmsnorm(streams, read, weight, eps, out_dtype, update=None, rows=None, shift=None):
     """RMSNorm of u = sum_s read[s] x_s over the residual streams x [S, T, H] (float32; ``read`` None: the plain sum).
     ``update`` (an object with y, gate [T, H] in the compute dtype, gate_bias [H], mix [S, S], write [S]) is put into the
     streams first, in the same kernel: x_t <- sum_s mix[s, t] x_s + write[t] * y * sigmoid(gate + gate_bias), every stream
     from the old ones.  rows=None: all rows, the streams updated in place; rows given: only those rows are read and
-    nothing is written back."""
+    nothing is written back.  ``shift`` = (mu [H], kept [seats, H] float32, state_slots): a step in which row i is request i's
+    one token; the token shift of the normed rows is then done in the same kernel and (rows, shifted rows) come back."""
     _need_cuda(streams, read, weight, rows)
     if streams.dim() != 3 or streams.dtype != torch.float32 or not streams.is_contiguous() or weight.dtype != torch.float32:
         raise TypeError("stream_rmsnorm: the residual streams are contiguous float32 [S, T, H], norm weights float32")
@@ -697,9 +701,19 @@ def stream_rmsnorm(streams, read, weight, eps, out_dtype, update=None, rows=None
                              "write [S] float32")
     n_out = T if rows is None else rows.numel()
     out = torch.empty((n_out, H), dtype=out_dtype, device=streams.device)
+    mu = kept = seats = shifted = None
+    if shift is not None:
+        mu, kept, seats = shift
+        _need_cuda(mu, kept, seats)
+        if rows is not None or mu.dtype != torch.float32 or mu.numel() != H or kept.dtype != torch.float32 or kept.stride(-1) != 1 \
+                or kept.shape[-1] < H or seats.numel() != T:
+            raise ValueError("stream_rmsnorm: the token shift takes all rows of a step of one token a request; mu float32 [H], kept float32 [seats, H]")
+        shifted = torch.empty((T, H), dtype=out_dtype, device=streams.device)
     _run(_core(), "fe_stream_rmsnorm", _ptr(streams), _c_int(S), _c_int(T), _c_int(H), _ptr(read), _ptr(weight), _c_float(eps), _ptr(y),
-         _ptr(gate), _ptr(gate_bias), _ptr(mix), _ptr(write), _ptr(rows), _c_int(n_out), _ptr(out), _c_int(_code(out_dtype)), _stream())
-    return out
+         _ptr(gate), _ptr(gate_bias), _ptr(mix), _ptr(write), _ptr(rows), _c_int(n_out), _ptr(out), _ptr(mu), _ptr(kept),
+         _c_ll(kept.stride(0) if kept is not None else 0), _ptr(seats), _c_int(kept.shape[0] if kept is not None else 0), _ptr(shifted),
+         _c_int(_code(out_dtype)), _stream())
+    return out if shift is None else (out, shifted)
 
 
 def token_shift(h, mu, kept, state_slots, cu_q, token_request):

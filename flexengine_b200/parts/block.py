@@ -198,9 +198,14 @@ class HyperGatedBlock:
 
     def forward(self, ctx, residual, pending, entry):
         from .streams import StreamUpdate
-        h = self.norm1.forward(ctx, residual, pending, read=self.hc1.read)
+        shift = self.shift.within_norm(ctx)
+        if shift is not None:                       # a decode step: norm and token shift are one kernel
+            h, shifted = self.norm1.forward(ctx, residual, pending, read=self.hc1.read, shift=shift)
+        else:
+            h = self.norm1.forward(ctx, residual, pending, read=self.hc1.read)
+            shifted = self.shift.forward(ctx, h)
         gate = self.rg1.logits(ctx, h)
-        y = self.mixer.forward(ctx, self.shift.forward(ctx, h), entry)
+        y = self.mixer.forward(ctx, shifted, entry)
         pending = StreamUpdate(y, gate, self.rg1.bias, self.hc1.mix, self.hc1.write)
         if self.feed_forward is None:
             return pending

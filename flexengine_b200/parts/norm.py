@@ -65,7 +65,11 @@ class StreamRMSNorm(Norm):
     def parameter_shapes(self) -> dict:
         return {"weight": ((self.hidden_size,), "vector")}
 
-    def forward(self, ctx, residual, delta, rows=None, read=None):
+    def forward(self, ctx, residual, delta, rows=None, read=None, shift=None):
+        """``shift`` = (mu, kept rows, state slots) in a step of one token a request: the token shift of the normed rows is
+        done in the same kernel, and (rows, shifted rows) come back."""
+        if shift is not None:
+            return ctx.ops.stream_rmsnorm(residual, read, self.weight, self.eps, ctx.dtype, update=delta, rows=rows, shift=shift)
         return ctx.ops.stream_rmsnorm(residual, read, self.weight, self.eps, ctx.dtype, update=delta, rows=rows)
 
 

@@ -56,6 +56,13 @@ class TokenShift(Part):
         kept = ctx.groups[self.group].state(self.slot)          # [seats, hidden] float32
         return ctx.ops.token_shift(h, self.mu, kept, ctx.state_slots, ctx.cu_q, ctx.token_request)
 
+    def within_norm(self, ctx):
+        """What the norm before needs to do this shift in its own kernel, in a step of one token a request on kernels that
+        can (row i is then request i's, and the row before it is the seat's kept one); None otherwise."""
+        if ctx.decode_only and getattr(ctx.ops, "FUSES_TOKEN_SHIFT", False):
+            return (self.mu, ctx.groups[self.group].state(self.slot), ctx.state_slots)
+        return None
+
 
 class StreamUpdate:
     __slots__ = ("y", "gate", "gate_bias", "mix", "write")

@@ -145,7 +145,10 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
 
 
 # ---- several residual streams, token shift, gated attention, minGRU ---------------------------------------
-def stream_rmsnorm(streams, read, weight, eps, out_dtype, update=None, rows=None):
+FUSES_TOKEN_SHIFT = True
+
+
+def stream_rmsnorm(streams, read, weight, eps, out_dtype, update=None, rows=None, shift=None):
     """u = sum_s read[s] x_s (read None: the plain sum) through an RMSNorm; ``update`` (y, gate, gate_bias, mix, write) is
     put into the streams first: x_t <- sum_s mix[s, t] x_s + write[t] * y * sigmoid(gate + gate_bias).  With ``rows``
     only those rows are read and nothing is written back."""
@@ -159,7 +162,18 @@ def stream_rmsnorm(streams, read, weight, eps, out_dtype, update=None, rows=None
         if rows is None:
             streams.copy_(x)
     u = x.sum(dim=0) if read is None else torch.einsum("s,snd->nd", read.float(), x)
-    return (u * torch.rsqrt(u.pow(2).mean(dim=-1, keepdim=True) + eps) * weight.float()).to(out_dtype)
+    out = (u * torch.rsqrt(u.pow(2).mean(dim=-1, keepdim=True) + eps) * weight.float()).to(out_dtype)
+    if shift is None:
+        return out
+    # a step of one token a request: row i is request i's; the token shift of the normed rows, on the rows as rounded
+    mu, kept, seats = shift
+    hf = out.float()
+    before = torch.zeros_like(hf)
+    for i, seat in enumerate(seats.tolist()):
+        if seat >= 0:
+            before[i] = kept[seat]
+            kept[seat] = hf[i]
+    return out, (hf + (before - hf) * mu.float()).to(out_dtype)
 
 
 def token_shift(h, mu, kept, state_slots, cu_q, token_request):

@@ -248,13 +248,27 @@ def test_stream_norm_and_update_alone(device, dtype, streams, width):
     ctx = types.SimpleNamespace(ops=ops, dtype=dt)
     update = StreamUpdate(y.to(device=device, dtype=dt), gate.to(device=device, dtype=dt), bias.to(device), mix.to(device), write.to(device))
     rows = torch.tensor([7, 0, 3], dtype=torch.int32, device=device)
-    streams_dev = x.to(device).contiguous()
+    streams_dev = x.clone().to(device).contiguous()
     some = norm.forward(ctx, streams_dev, update, rows=rows, read=read.to(device))
     assert torch.equal(streams_dev.cpu(), x)                                  # nothing was written back
     close(some, want[rows.long().cpu()], dtype, "chosen rows", bars=(2e-5, 3e-2))
     got = norm.forward(ctx, streams_dev, update, read=read.to(device))
     close(got, want, dtype, "all rows", bars=(2e-5, 3e-2))
     assert (streams_dev.double().cpu() - new).abs().max() < 1e-4 * float(new.abs().max())
+    # a step of one token a request: the token shift of the normed rows in the same kernel; a seat below 0 keeps nothing
+    mu = randn(D, seed=9)
+    kept_before = randn(T + 2, D, seed=10)
+    kept = kept_before.clone().to(device)
+    seats = torch.tensor([4, -1, 0, 9, 2, 10, 1, 7, 3], dtype=torch.int32, device=device)
+    again = x.clone().to(device).contiguous()
+    rows_out, shifted = norm.forward(ctx, again, update, read=read.to(device), shift=(mu.to(device), kept, seats))
+    close(rows_out, want, dtype, "rows beside their shift", bars=(2e-5, 3e-2))
+    before = torch.stack([kept_before[seat] if seat >= 0 else torch.zeros(D) for seat in seats.tolist()]).to(F64)
+    close(shifted, want + (before - want) * mu.to(F64), dtype, "shifted rows", bars=(2e-5, 3e-2))
+    for i, seat in enumerate(seats.tolist()):
+        if seat >= 0:
+            assert torch.equal(kept[seat].cpu(), rows_out[i].float().cpu())
+    assert torch.equal(kept[5].cpu(), kept_before[5]) and torch.equal(kept[8].cpu(), kept_before[8])       # nobody's seats
     # no update and the plain sum: what the model's last norm does when nothing is pending
     plain_sum = norm.forward(ctx, streams_dev, None, rows=rows)
     close(plain_sum, plain.rms_norm(new.sum(dim=0), eps, weight.to(F64))[rows.long().cpu()], dtype, "plain sum", bars=(2e-5, 3e-2))
